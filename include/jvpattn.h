@@ -1,0 +1,120 @@
+/*
+ * jvpattn - C ABI of the B200 (sm_100a) flash-attention JVP kernels.
+ *
+ * The library replaces the three GPU entry points that the reference's autograd glue
+ * (semicat/jvp_utils/functional.py) calls:
+ *
+ *   jvpattn_fwd   <- flash_attention_jvp_multihead_triton_kernel_wrapper
+ *                    (semicat/jvp_utils/ryu_triton.py:295-422, called at functional.py:28-40)
+ *   jvpattn_bwd   <- _flash_attn_backward of the tangent output
+ *                    (semicat/jvp_utils/flash_jvp_backward.py:2293-2714, called at functional.py:131-149)
+ *                    and _flash_attn_backward of the primal output
+ *                    (semicat/jvp_utils/flash_attn_triton.py:974-1093, called at functional.py:192-205),
+ *                    merged: either cotangent may be NULL.
+ *
+ * Conventions
+ *   - plain C types only; every pointer is a CUDA device pointer owned by the caller, except where noted.
+ *   - the library allocates no device memory; scratch is passed in (jvpattn_bwd_workspace_bytes).
+ *   - kernels are enqueued on `stream` (a cudaStream_t cast to void*) of the CURRENT device; no host sync.
+ *   - return value 0 on success, a negative JVPATTN_E* code otherwise; nothing is thrown.
+ *   - there is no CPU path: without a usable sm_100 device every compute call returns JVPATTN_EARCH.
+ */
+#ifndef JVPATTN_H_
+#define JVPATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JVPATTN_ABI_VERSION 1
+
+enum {
+  JVPATTN_OK = 0,
+  JVPATTN_EINVAL = -1,    /* NULL where a tensor is required, bad dims, bad dtype             */
+  JVPATTN_ESTRIDE = -2,   /* innermost stride != 1                                            */
+  JVPATTN_EALIGN = -3,    /* base pointer or a stride not 16-byte aligned                     */
+  JVPATTN_EHEADDIM = -4,  /* head dim outside [16, 128] (ryu_triton.py:319-322, flash_jvp_backward.py:2318) */
+  JVPATTN_ESTAT = -5,     /* row-statistic length not a multiple of 128 or < Lq (functional.py:124-125)     */
+  JVPATTN_EWORKSPACE = -6,/* workspace NULL or smaller than jvpattn_bwd_workspace_bytes()     */
+  JVPATTN_EARCH = -7,     /* no CUDA device, or the device is not sm_100                      */
+  JVPATTN_ELAUNCH = -8,   /* the CUDA runtime refused a launch; see jvpattn_last_cuda_error() */
+  JVPATTN_EDEVICE = -9    /* a bounded device-side wait ran out; see jvpattn_device_status()  */
+};
+
+enum { JVPATTN_BF16 = 0, JVPATTN_FP16 = 1 };
+
+/* Selects the kernel family.  AUTO picks the tcgen05/TMA kernels whenever the shape allows and the
+ * portable SIMT kernels otherwise; the other two force one family (the forced tcgen05 choice returns
+ * JVPATTN_EINVAL for a shape it cannot run).  Used by the parity tests to check one family against
+ * the other on the device. */
+enum { JVPATTN_KERNELS_AUTO = 0, JVPATTN_KERNELS_SIMT = 1, JVPATTN_KERNELS_TCGEN05 = 2 };
+
+/* A 4-D tensor indexed (batch, head, position, channel) with element strides; stride[3] must be 1.
+ * The reference passes (B,H,S,D) views of (B,S,H,D)-contiguous memory (functional.py:324-326), so
+ * stride[1] < stride[2] is the common case. */
+typedef struct {
+  void *ptr;
+  int64_t stride[4];
+} jvpattn_tensor;
+
+typedef struct {
+  int32_t batch, heads;
+  int32_t len_q, len_k;
+  int32_t head_dim;
+  int32_t stat_len;  /* allocated row length of lse / mu / li: ceil(len_q/128)*128 (functional.py:57-59, 229-230) */
+  int32_t dtype;     /* JVPATTN_BF16 or JVPATTN_FP16 for every jvpattn_tensor */
+  int32_t kernels;   /* JVPATTN_KERNELS_* */
+  float scale;       /* softmax scale; <= 0 selects 1/sqrt(head_dim) (ryu_triton.py:324-325) */
+} jvpattn_problem;
+
+/* Fused forward: O = softmax(scale QK^T) V together with its tangent Od along (tq, tk, tv), and the row
+ * statistics lse = logsumexp(s) (the reference's M), mu = E_P[sd] (its MU); li (its LI, the softmax
+ * denominator) is written only when non-NULL.  lse/mu/li are float32 [batch, heads, stat_len]; rows
+ * >= len_q are not written.  o and to are written in place. */
+int jvpattn_fwd(const jvpattn_problem *p,
+                const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                const jvpattn_tensor *o, const jvpattn_tensor *to,
+                float *lse, float *mu, float *li, void *stream);
+
+/* Bytes of scratch jvpattn_bwd needs for this problem (row dot products and float32 accumulators for
+ * dq / dtq).  Returns 0 for an invalid problem. */
+size_t jvpattn_bwd_workspace_bytes(const jvpattn_problem *p);
+
+/* Backward: VJP of cotangents g_o (on O) and g_to (on Od) with respect to q, k, v, tq, tk, tv.
+ * Either cotangent may be NULL (treated as zero) but not both.  dq, dk, dv are always written.
+ * tq, tk, tv, to, mu, dtq, dtk, dtv are required when g_to is given; when it is NULL they are ignored
+ * (may be NULL) and no tangent gradient is written.
+ * `workspace` need not be initialised. */
+int jvpattn_bwd(const jvpattn_problem *p,
+                const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                const jvpattn_tensor *o, const jvpattn_tensor *to,
+                const jvpattn_tensor *g_o, const jvpattn_tensor *g_to,
+                const float *lse, const float *mu,
+                const jvpattn_tensor *dq, const jvpattn_tensor *dk, const jvpattn_tensor *dv,
+                const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
+                void *workspace, size_t workspace_bytes, void *stream);
+
+/* Which kernel family AUTO resolves to for this problem (JVPATTN_KERNELS_SIMT or _TCGEN05), for the
+ * forward (which = 0) or the backward (which = 1); negative error code for an invalid problem. */
+int jvpattn_selected_kernels(const jvpattn_problem *p, int which);
+
+/* Number of kernels this library has launched in the calling process (all threads). */
+uint64_t jvpattn_launch_count(void);
+
+/* Synchronises the current device and returns the device-side status word: 0 if no bounded wait has
+ * run out since the last call, else a code identifying the wait that gave up.  Clears the word. */
+int jvpattn_device_status(void);
+
+const char *jvpattn_strerror(int code);
+const char *jvpattn_last_cuda_error(void); /* text of the last CUDA runtime error seen by this thread */
+int jvpattn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JVPATTN_H_ */

@@ -1,0 +1,143 @@
+"""ctypes binding of ``libjvpattn.so`` (the C ABI declared in ``include/jvpattn.h``).
+
+The shared library is built in-tree with ``nvcc`` for sm_100a by :func:`build` and loaded from this
+package's directory.  There is no fallback of any kind: if the library cannot be loaded, or the
+device is not a B200, every compute call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import shutil
+import subprocess
+import threading
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_CSRC = os.path.join(_PKG_DIR, "csrc")
+LIB_PATH = os.path.join(_PKG_DIR, "libjvpattn.so")
+SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+BF16, FP16 = 0, 1
+KERNELS_AUTO, KERNELS_SIMT, KERNELS_TCGEN05 = 0, 1, 2
+
+EXPORTS = (
+    "jvpattn_fwd", "jvpattn_bwd", "jvpattn_bwd_workspace_bytes", "jvpattn_selected_kernels",
+    "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
+    "jvpattn_abi_version",
+)
+
+
+class Tensor4(ctypes.Structure):
+    """``jvpattn_tensor``: device pointer + element strides in (batch, head, position, channel) order."""
+    _fields_ = [("ptr", ctypes.c_void_p), ("stride", ctypes.c_int64 * 4)]
+
+
+class Problem(ctypes.Structure):
+    """``jvpattn_problem``."""
+    _fields_ = [
+        ("batch", ctypes.c_int32), ("heads", ctypes.c_int32),
+        ("len_q", ctypes.c_int32), ("len_k", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32), ("stat_len", ctypes.c_int32),
+        ("dtype", ctypes.c_int32), ("kernels", ctypes.c_int32),
+        ("scale", ctypes.c_float),
+    ]
+
+
+class JvpAttnError(RuntimeError):
+    def __init__(self, code: int, where: str, detail: str = ""):
+        self.code = code
+        super().__init__(f"{where} failed with code {code}: {detail}")
+
+
+def _sources_newer_than_lib() -> bool:
+    if not os.path.exists(LIB_PATH):
+        return True
+    t = os.path.getmtime(LIB_PATH)
+    deps = [os.path.join(_CSRC, f) for f in os.listdir(_CSRC)] + [
+        os.path.join(os.path.dirname(_PKG_DIR), "include", "jvpattn.h")]
+    return any(os.path.getmtime(d) > t for d in deps if os.path.isfile(d))
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile ``libjvpattn.so`` for sm_100a with nvcc (cross-compiles without a GPU)."""
+    if not force and not _sources_newer_than_lib():
+        return LIB_PATH
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found: cannot build libjvpattn.so")
+    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH + ".tmp", *[os.path.join(_CSRC, s) for s in SOURCES]]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    os.replace(LIB_PATH + ".tmp", LIB_PATH)
+    if verbose:
+        print(proc.stderr)
+    return LIB_PATH
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> ctypes.CDLL:
+    """Load the library (once) and declare the prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(or semicat_b200._lib.build()).  There is no CPU or PyTorch fallback for these kernels.")
+        lib = ctypes.CDLL(LIB_PATH)
+        T = ctypes.POINTER(Tensor4)
+        P = ctypes.POINTER(Problem)
+        F = ctypes.c_void_p  # float* device pointers are passed as integers
+        lib.jvpattn_fwd.argtypes = [P] + [T] * 8 + [F, F, F, ctypes.c_void_p]
+        lib.jvpattn_fwd.restype = ctypes.c_int
+        lib.jvpattn_bwd.argtypes = [P] + [T] * 10 + [F, F] + [T] * 6 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        lib.jvpattn_bwd.restype = ctypes.c_int
+        lib.jvpattn_bwd_workspace_bytes.argtypes = [P]
+        lib.jvpattn_bwd_workspace_bytes.restype = ctypes.c_size_t
+        lib.jvpattn_selected_kernels.argtypes = [P, ctypes.c_int]
+        lib.jvpattn_selected_kernels.restype = ctypes.c_int
+        lib.jvpattn_launch_count.argtypes = []
+        lib.jvpattn_launch_count.restype = ctypes.c_uint64
+        lib.jvpattn_device_status.argtypes = []
+        lib.jvpattn_device_status.restype = ctypes.c_int
+        lib.jvpattn_strerror.argtypes = [ctypes.c_int]
+        lib.jvpattn_strerror.restype = ctypes.c_char_p
+        lib.jvpattn_last_cuda_error.argtypes = []
+        lib.jvpattn_last_cuda_error.restype = ctypes.c_char_p
+        lib.jvpattn_abi_version.argtypes = []
+        lib.jvpattn_abi_version.restype = ctypes.c_int
+        if lib.jvpattn_abi_version() != 1:
+            raise RuntimeError("libjvpattn.so ABI version mismatch; rebuild it")
+        _lib = lib
+    return _lib
+
+
+def check(code: int, where: str) -> None:
+    if code == 0:
+        return
+    lib = load()
+    detail = lib.jvpattn_strerror(code).decode()
+    if code == -8:
+        detail += " [" + lib.jvpattn_last_cuda_error().decode() + "]"
+    raise JvpAttnError(code, where, detail)
+
+
+def launch_count() -> int:
+    return int(load().jvpattn_launch_count())
+
+
+def device_status() -> int:
+    return int(load().jvpattn_device_status())

@@ -1,0 +1,273 @@
+// extern "C" entry points of libjvpattn: argument validation, kernel-family selection, launch.
+// No torch types, no device allocation, no host synchronisation (except jvpattn_device_status).
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "jvpattn_common.cuh"
+
+namespace jvpattn {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Written by a kernel whose bounded wait ran out; read and cleared by jvpattn_device_status().
+__device__ unsigned int g_status_word = 0;
+
+namespace {
+
+thread_local char t_cuda_error[256] = "";
+
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  int state = 0;  // 0 unknown, 1 usable sm_100, -1 unusable
+  unsigned int *status = nullptr;
+};
+DeviceInfo g_devices[kMaxDevices];
+std::mutex g_device_mutex;
+
+int note_cuda(cudaError_t e) {
+  if (e == cudaSuccess) return JVPATTN_OK;
+  std::snprintf(t_cuda_error, sizeof(t_cuda_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+  (void)cudaGetLastError();
+  return JVPATTN_ELAUNCH;
+}
+
+// Resolves the current device once: compute capability and the address of its status word.
+int current_device(DeviceInfo **out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    note_cuda(e);
+    return JVPATTN_EARCH;
+  }
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  DeviceInfo &d = g_devices[dev];
+  if (d.state == 0) {
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess || major != 10) {
+      note_cuda(e);
+      d.state = -1;
+    } else {
+      void *p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_status_word);
+      if (e != cudaSuccess) {
+        note_cuda(e);
+        d.state = -1;
+      } else {
+        d.status = static_cast<unsigned int *>(p);
+        d.state = 1;
+      }
+    }
+  }
+  if (d.state != 1) return JVPATTN_EARCH;
+  *out = &d;
+  return JVPATTN_OK;
+}
+
+int check_problem(const jvpattn_problem *p) {
+  if (!p) return JVPATTN_EINVAL;
+  if (p->batch < 0 || p->heads < 0 || p->len_q < 0 || p->len_k < 0) return JVPATTN_EINVAL;
+  if (p->dtype != JVPATTN_BF16 && p->dtype != JVPATTN_FP16) return JVPATTN_EINVAL;
+  if (p->kernels < JVPATTN_KERNELS_AUTO || p->kernels > JVPATTN_KERNELS_TCGEN05) return JVPATTN_EINVAL;
+  if (p->head_dim < 16 || p->head_dim > 128) return JVPATTN_EHEADDIM;
+  if (p->stat_len < p->len_q || p->stat_len % 128 != 0) return JVPATTN_ESTAT;
+  if (p->len_k == 0 && p->len_q > 0 && p->batch > 0 && p->heads > 0) return JVPATTN_EINVAL;  // softmax over nothing
+  if (!(p->scale == p->scale)) return JVPATTN_EINVAL;
+  return JVPATTN_OK;
+}
+
+bool is_empty(const jvpattn_problem *p) { return p->batch == 0 || p->heads == 0 || (p->len_q == 0 && p->len_k == 0); }
+
+int to_view(const jvpattn_tensor *t, bool required, View *v) {
+  if (!t || !t->ptr) {
+    if (required) return JVPATTN_EINVAL;
+    *v = View{nullptr, 0, 0, 0};
+    return JVPATTN_OK;
+  }
+  if (t->stride[3] != 1) return JVPATTN_ESTRIDE;
+  if (reinterpret_cast<uintptr_t>(t->ptr) % 2 != 0) return JVPATTN_EALIGN;
+  *v = View{t->ptr, t->stride[0], t->stride[1], t->stride[2]};
+  return JVPATTN_OK;
+}
+
+float effective_scale(const jvpattn_problem *p) {
+  return p->scale > 0.f ? p->scale : 1.0f / std::sqrt((float)p->head_dim);
+}
+
+#define JVP_TRY(expr)            \
+  do {                           \
+    int rc__ = (expr);           \
+    if (rc__ != JVPATTN_OK) return rc__; \
+  } while (0)
+
+int build_fwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+              const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+              const jvpattn_tensor *o, const jvpattn_tensor *to, float *lse, float *mu, float *li, FwdArgs *a) {
+  JVP_TRY(check_problem(p));
+  JVP_TRY(to_view(q, true, &a->q));
+  JVP_TRY(to_view(k, true, &a->k));
+  JVP_TRY(to_view(v, true, &a->v));
+  JVP_TRY(to_view(tq, true, &a->tq));
+  JVP_TRY(to_view(tk, true, &a->tk));
+  JVP_TRY(to_view(tv, true, &a->tv));
+  JVP_TRY(to_view(o, true, &a->o));
+  JVP_TRY(to_view(to, true, &a->to));
+  if (!lse || !mu) return JVPATTN_EINVAL;
+  a->lse = lse; a->mu = mu; a->li = li;
+  a->B = p->batch; a->H = p->heads; a->Lq = p->len_q; a->Lk = p->len_k; a->D = p->head_dim;
+  a->stat_len = p->stat_len; a->dtype = p->dtype; a->scale = effective_scale(p);
+  a->status = nullptr;
+  return JVPATTN_OK;
+}
+
+int build_bwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+              const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+              const jvpattn_tensor *o, const jvpattn_tensor *to, const jvpattn_tensor *g_o, const jvpattn_tensor *g_to,
+              const float *lse, const float *mu, const jvpattn_tensor *dq, const jvpattn_tensor *dk,
+              const jvpattn_tensor *dv, const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
+              BwdArgs *a) {
+  JVP_TRY(check_problem(p));
+  JVP_TRY(to_view(g_o, false, &a->g_o));
+  JVP_TRY(to_view(g_to, false, &a->g_to));
+  if (!a->g_o.ptr && !a->g_to.ptr) return JVPATTN_EINVAL;
+  const bool need_t = a->g_to.ptr != nullptr;
+  JVP_TRY(to_view(q, true, &a->q));
+  JVP_TRY(to_view(k, true, &a->k));
+  JVP_TRY(to_view(v, true, &a->v));
+  JVP_TRY(to_view(o, true, &a->o));
+  JVP_TRY(to_view(tq, need_t, &a->tq));
+  JVP_TRY(to_view(tk, need_t, &a->tk));
+  JVP_TRY(to_view(tv, need_t, &a->tv));
+  JVP_TRY(to_view(to, need_t, &a->to));
+  JVP_TRY(to_view(dq, true, &a->dq));
+  JVP_TRY(to_view(dk, true, &a->dk));
+  JVP_TRY(to_view(dv, true, &a->dv));
+  JVP_TRY(to_view(dtq, need_t, &a->dtq));
+  JVP_TRY(to_view(dtk, need_t, &a->dtk));
+  JVP_TRY(to_view(dtv, need_t, &a->dtv));
+  if (!lse || (need_t && !mu)) return JVPATTN_EINVAL;
+  if (!need_t) {
+    // Without a cotangent on the tangent output nothing depends on the tangents or on mu: every term
+    // they enter is multiplied by an exact zero.  Point the unused views at valid memory.
+    a->tq = a->q; a->tk = a->k; a->tv = a->v; a->to = a->o;
+    a->dtq = a->dtk = a->dtv = View{nullptr, 0, 0, 0};
+    mu = lse;
+  }
+  a->lse = lse; a->mu = mu;
+  a->B = p->batch; a->H = p->heads; a->Lq = p->len_q; a->Lk = p->len_k; a->D = p->head_dim;
+  a->stat_len = p->stat_len; a->dtype = p->dtype; a->scale = effective_scale(p);
+  a->workspace = nullptr; a->workspace_bytes = 0; a->status = nullptr;
+  return JVPATTN_OK;
+}
+
+}  // namespace
+}  // namespace jvpattn
+
+using namespace jvpattn;
+
+extern "C" {
+
+int jvpattn_abi_version(void) { return JVPATTN_ABI_VERSION; }
+
+uint64_t jvpattn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char *jvpattn_last_cuda_error(void) { return t_cuda_error; }
+
+const char *jvpattn_strerror(int code) {
+  switch (code) {
+    case JVPATTN_OK: return "ok";
+    case JVPATTN_EINVAL: return "invalid argument (null tensor, negative size, empty key axis, unknown dtype or kernel family, or a shape the forced kernel family cannot run)";
+    case JVPATTN_ESTRIDE: return "innermost stride must be 1";
+    case JVPATTN_EALIGN: return "pointer or stride alignment not supported";
+    case JVPATTN_EHEADDIM: return "head_dim must be in [16, 128]";
+    case JVPATTN_ESTAT: return "row-statistic length must be a multiple of 128 and >= len_q";
+    case JVPATTN_EWORKSPACE: return "workspace missing or too small (see jvpattn_bwd_workspace_bytes)";
+    case JVPATTN_EARCH: return "no usable CUDA device: this library runs on sm_100 (B200) only and has no CPU path";
+    case JVPATTN_ELAUNCH: return "CUDA launch failed (see jvpattn_last_cuda_error)";
+    case JVPATTN_EDEVICE: return "a bounded device-side wait ran out";
+    default: return "unknown jvpattn error code";
+  }
+}
+
+int jvpattn_device_status(void) {
+  DeviceInfo *d = nullptr;
+  int rc = current_device(&d);
+  if (rc != JVPATTN_OK) return rc;
+  unsigned int word = 0, zero = 0;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpy(&word, d->status, sizeof(word), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && word != 0) e = cudaMemcpy(d->status, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return note_cuda(e);
+  return (int)word;
+}
+
+int jvpattn_selected_kernels(const jvpattn_problem *p, int which) {
+  int rc = check_problem(p);
+  if (rc != JVPATTN_OK) return rc;
+  if (p->kernels != JVPATTN_KERNELS_AUTO) return p->kernels;
+  // Shape-only decision with ideally aligned tensors; a misaligned call still falls back to SIMT.
+  if (which == 0) {
+    FwdArgs a{};
+    a.B = p->batch; a.H = p->heads; a.Lq = p->len_q; a.Lk = p->len_k; a.D = p->head_dim; a.dtype = p->dtype;
+    a.stat_len = p->stat_len;
+    const int64_t sl = p->head_dim;
+    a.q = a.k = a.v = a.tq = a.tk = a.tv = a.o = a.to = View{(void *)16, sl * p->len_q, sl * p->len_q * p->batch, sl};
+    return sm100_fwd_supported(a) ? JVPATTN_KERNELS_TCGEN05 : JVPATTN_KERNELS_SIMT;
+  }
+  BwdArgs a{};
+  a.B = p->batch; a.H = p->heads; a.Lq = p->len_q; a.Lk = p->len_k; a.D = p->head_dim; a.dtype = p->dtype;
+  a.stat_len = p->stat_len;
+  const int64_t sl = p->head_dim;
+  View any{(void *)16, sl * p->len_q, sl * p->len_q * p->batch, sl};
+  a.q = a.k = a.v = a.tq = a.tk = a.tv = a.o = a.to = a.g_o = a.g_to = a.dq = a.dk = a.dv = a.dtq = a.dtk = a.dtv = any;
+  return sm100_bwd_supported(a) ? JVPATTN_KERNELS_TCGEN05 : JVPATTN_KERNELS_SIMT;
+}
+
+int jvpattn_fwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                const jvpattn_tensor *o, const jvpattn_tensor *to, float *lse, float *mu, float *li, void *stream) {
+  FwdArgs a{};
+  JVP_TRY(build_fwd(p, q, k, v, tq, tk, tv, o, to, lse, mu, li, &a));
+  DeviceInfo *d = nullptr;
+  JVP_TRY(current_device(&d));
+  if (is_empty(p) || p->len_q == 0) return JVPATTN_OK;
+  a.status = d->status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  bool fast = p->kernels != JVPATTN_KERNELS_SIMT && sm100_fwd_supported(a);
+  if (p->kernels == JVPATTN_KERNELS_TCGEN05 && !fast) return JVPATTN_EINVAL;
+  return note_cuda(fast ? sm100_fwd(a, s) : simt_fwd(a, s));
+}
+
+size_t jvpattn_bwd_workspace_bytes(const jvpattn_problem *p) {
+  if (check_problem(p) != JVPATTN_OK) return 0;
+  return sm100_bwd_workspace_bytes(p->batch, p->heads, p->len_q, p->len_k, p->head_dim, p->stat_len);
+}
+
+int jvpattn_bwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                const jvpattn_tensor *o, const jvpattn_tensor *to, const jvpattn_tensor *g_o, const jvpattn_tensor *g_to,
+                const float *lse, const float *mu, const jvpattn_tensor *dq, const jvpattn_tensor *dk,
+                const jvpattn_tensor *dv, const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
+                void *workspace, size_t workspace_bytes, void *stream) {
+  BwdArgs a{};
+  JVP_TRY(build_bwd(p, q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv, dtq, dtk, dtv, &a));
+  size_t need = jvpattn_bwd_workspace_bytes(p);
+  if (need > 0 && (!workspace || workspace_bytes < need)) return JVPATTN_EWORKSPACE;
+  if (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return JVPATTN_EALIGN;
+  DeviceInfo *d = nullptr;
+  JVP_TRY(current_device(&d));
+  if (is_empty(p)) return JVPATTN_OK;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  a.status = d->status;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  bool fast = p->kernels != JVPATTN_KERNELS_SIMT && sm100_bwd_supported(a);
+  if (p->kernels == JVPATTN_KERNELS_TCGEN05 && !fast) return JVPATTN_EINVAL;
+  return note_cuda(fast ? sm100_bwd(a, s) : simt_bwd(a, s));
+}
+
+}  // extern "C"

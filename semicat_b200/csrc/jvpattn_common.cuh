@@ -1,0 +1,67 @@
+// Shared declarations of the jvpattn kernels: the validated problem description that the C-ABI layer
+// hands to the kernel launchers, and small device helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jvpattn.h"
+
+namespace jvpattn {
+
+// A (B,H,L,D) view with unit innermost stride.  Strides are in elements.
+struct View {
+  void *ptr;
+  int64_t sb, sh, sl;
+  __host__ __device__ __forceinline__ int64_t offset(int b, int h, int l) const {
+    return (int64_t)b * sb + (int64_t)h * sh + (int64_t)l * sl;
+  }
+};
+
+struct FwdArgs {
+  View q, k, v, tq, tk, tv, o, to;
+  float *lse, *mu, *li;  // li may be null
+  unsigned int *status;  // device status word, set when a bounded wait runs out
+  int B, H, Lq, Lk, D, stat_len;
+  int dtype;
+  float scale;
+};
+
+struct BwdArgs {
+  View q, k, v, tq, tk, tv, o, to;
+  View g_o, g_to;  // ptr == nullptr when the cotangent is absent
+  View dq, dk, dv, dtq, dtk, dtv;
+  const float *lse, *mu;
+  void *workspace;
+  size_t workspace_bytes;
+  unsigned int *status;
+  int B, H, Lq, Lk, D, stat_len;
+  int dtype;
+  float scale;
+};
+
+// launchers (each returns a cudaError_t from the launch; they never synchronise)
+cudaError_t simt_fwd(const FwdArgs &a, cudaStream_t stream);
+cudaError_t simt_bwd(const BwdArgs &a, cudaStream_t stream);
+
+bool sm100_fwd_supported(const FwdArgs &a);
+bool sm100_bwd_supported(const BwdArgs &a);
+cudaError_t sm100_fwd(const FwdArgs &a, cudaStream_t stream);
+cudaError_t sm100_bwd(const BwdArgs &a, cudaStream_t stream);
+size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_len);
+
+void count_launches(int n);
+
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f(float x) { return __float2half_rn(x); }
+};
+
+}  // namespace jvpattn

@@ -1,0 +1,121 @@
+"""GPU parity: the CUDA kernels, called through the C ABI, against the CPU oracle and the golden fixtures.
+
+Tolerance for bf16/fp16 kernels against the fp32/fp64 oracle evaluated on the same (rounded) inputs:
+|x - ref| <= 1e-2 + 2e-2 |ref| for O, Od and all six gradients."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    import gpu_util as G
+    from semicat_b200 import _lib, ops
+
+FAMILIES = {"auto": 0, "simt": 1}
+MODES = ("both", "tan", "pri")
+
+
+def _golden_dtype(case):
+    return torch.float16 if case.startswith("selftest") else torch.bfloat16
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("case", GOLDEN_CASES)
+def test_golden_fixtures(case, mode, family):
+    g = load_golden(case)
+    dtype = _golden_dtype(case)
+    ins = G.rounded({n: g[n] for n in (*G.IN_NAMES, "g_o", "g_od")}, dtype)
+    got = G.run(ins, dtype=dtype, kernels=FAMILIES[family], mode=mode)
+    if case != "c1_fp32":
+        # inputs of these fixtures are exactly representable: compare with the reference's own outputs
+        want = {"o": g["o"], "to": g["od"], "lse": g["lse"], "mu": g["mu"]}
+        want.update({n: g[f"{n}_{mode}"] for n in G.GRAD_NAMES})
+    else:
+        want = G.oracle(ins, mode)  # fp32 fixture: oracle re-evaluated on the bf16-rounded inputs
+    G.compare(got, want, mode, f"{case}/{mode}/{family}")
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+@pytest.mark.parametrize("layout", ["bshd", "padded"])
+@pytest.mark.parametrize("shape", [(2, 3, 128, 128, 64), (1, 2, 200, 72, 32), (1, 2, 256, 384, 128), (2, 1, 33, 1, 16)])
+def test_layouts_and_ragged_shapes(shape, layout, family):
+    B, H, Lq, Lk, D = shape
+    ins = G.rounded(G.synth(B, H, Lq, Lk, D, seed=11), torch.bfloat16)
+    got = G.run(ins, kernels=FAMILIES[family], layout=layout, mode="both")
+    G.compare(got, G.oracle(ins, "both"), "both", f"{shape}/{layout}/{family}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("L", [128, 256, 1024])
+@pytest.mark.parametrize("D", [64, 128])
+def test_auto_family_against_oracle(D, L, dtype):
+    ins = G.rounded(G.synth(2, 2, L, L, D, seed=L + D), dtype)
+    for mode in MODES:
+        got = G.run(ins, dtype=dtype, mode=mode)
+        G.compare(got, G.oracle(ins, mode), mode, f"L{L} D{D} {dtype} {mode}")
+
+
+def test_unit_normal_inputs_long_sequence():
+    """Value distribution of the long-sequence sweep: N(0,1) primals AND tangents (scores have std ~1
+    after scaling only because scale = 1/sqrt(d); q is not pre-scaled)."""
+    ins = G.rounded(G.synth(1, 2, 2048, 2048, 64, seed=5, q_scale=1.0, t_scale=1.0), torch.bfloat16)
+    got = G.run(ins, mode="both")
+    want = G.oracle(ins, "both")
+    # gradients reach magnitudes of tens here; the bar is relative-dominated
+    G.compare(got, want, "both", "sweep-distribution")
+
+
+def test_explicit_scale_and_empty_batch():
+    ins = G.rounded(G.synth(1, 1, 128, 128, 64, seed=2), torch.bfloat16)
+    got = G.run(ins, mode="both", scale=0.2)
+    G.compare(got, G.oracle(ins, "both", scale=0.2), "both", "scale=0.2")
+    empty = {n: np.zeros((0, 2, 128, 64), np.float32) for n in (*G.IN_NAMES, "g_o", "g_od")}
+    G.run(empty, mode="both")  # no launch, no error
+
+
+def test_full_size_microbench_shape_properties():
+    """BASELINE config 2 (B64 H12 L128 d64) at full size: (1) Od is linear in the tangents, (2) with zero
+    tangents Od vanishes and O is unchanged, (3) a sample of heads matches the oracle."""
+    B, H, L, D = 64, 12, 128, 64
+    ins = G.rounded(G.synth(B, H, L, L, D, seed=0), torch.bfloat16)
+    base = G.run(ins, mode="both")
+    zero = dict(ins, tq=np.zeros_like(ins["tq"]), tk=np.zeros_like(ins["tk"]), tv=np.zeros_like(ins["tv"]))
+    z = G.run(zero, mode=None)
+    assert np.abs(z["to"]).max() == 0.0
+    assert np.array_equal(z["o"], base["o"])
+    dbl = dict(ins, tq=2 * ins["tq"], tk=2 * ins["tk"], tv=2 * ins["tv"])  # exact in bf16
+    d = G.run(dbl, mode=None)
+    G.assert_close(d["to"], 2 * base["to"], "linearity", rtol=2e-2, atol=1e-2)
+    sel = (slice(0, 64, 21), slice(0, 12, 5))
+    sub = {n: x[sel] for n, x in ins.items()}
+    want = G.oracle(sub, "both")
+    G.compare({n: x[sel] for n, x in base.items()}, want, "both", "config2-sample")
+
+
+def test_run_to_run_determinism_of_forward():
+    ins = G.rounded(G.synth(2, 2, 256, 256, 64, seed=9), torch.bfloat16)
+    a = G.run(ins, mode=None)
+    b = G.run(ins, mode=None)
+    for n in ("o", "to", "lse", "mu"):
+        assert np.array_equal(a[n], b[n]), n
+
+
+def test_library_really_launched_and_status_clean():
+    before = _lib.launch_count()
+    ins = G.rounded(G.synth(1, 1, 128, 128, 64, seed=1), torch.bfloat16)
+    G.run(ins, mode="both")
+    assert _lib.launch_count() > before
+    assert _lib.device_status() == 0
+
+
+def test_forced_tcgen05_rejects_what_it_cannot_run():
+    ins = G.rounded(G.synth(1, 1, 40, 40, 16, seed=1), torch.bfloat16)
+    if ops.selected_kernels(1, 1, 40, 40, 16) == ops.KERNELS_TCGEN05:
+        pytest.skip("shape is supported by the tcgen05 kernels")
+    with pytest.raises(_lib.JvpAttnError) as e:
+        G.run(ins, kernels=ops.KERNELS_TCGEN05, mode=None)
+    assert e.value.code == -1
