@@ -15,7 +15,8 @@ import threading
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG_DIR, "csrc")
 LIB_PATH = os.path.join(_PKG_DIR, "libjvpattn.so")
-SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu"]
+SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu",
+           "sm100_tensormap.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",

@@ -231,10 +231,11 @@ int jvpattn_fwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn
                 const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
                 const jvpattn_tensor *o, const jvpattn_tensor *to, float *lse, float *mu, float *li, void *stream) {
   FwdArgs a{};
+  JVP_TRY(check_problem(p));
+  if (is_empty(p) || p->len_q == 0) return JVPATTN_OK;  // nothing to write; pointers of empty tensors may be NULL
   JVP_TRY(build_fwd(p, q, k, v, tq, tk, tv, o, to, lse, mu, li, &a));
   DeviceInfo *d = nullptr;
   JVP_TRY(current_device(&d));
-  if (is_empty(p) || p->len_q == 0) return JVPATTN_OK;
   a.status = d->status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   bool fast = p->kernels != JVPATTN_KERNELS_SIMT && sm100_fwd_supported(a);
@@ -254,13 +255,14 @@ int jvpattn_bwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn
                 const jvpattn_tensor *dv, const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
                 void *workspace, size_t workspace_bytes, void *stream) {
   BwdArgs a{};
+  JVP_TRY(check_problem(p));
+  if (is_empty(p)) return JVPATTN_OK;
   JVP_TRY(build_bwd(p, q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv, dtq, dtk, dtv, &a));
   size_t need = jvpattn_bwd_workspace_bytes(p);
   if (need > 0 && (!workspace || workspace_bytes < need)) return JVPATTN_EWORKSPACE;
   if (workspace && reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return JVPATTN_EALIGN;
   DeviceInfo *d = nullptr;
   JVP_TRY(current_device(&d));
-  if (is_empty(p)) return JVPATTN_OK;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
   a.status = d->status;

@@ -1,5 +1,349 @@
+// Fused attention-JVP forward for sm_100a: O = softmax(s) V and Od = (P o (sd - mu)) V + P Vd in one pass,
+// tcgen05 MMAs accumulating in TMEM, TMA-staged operand tiles, online softmax.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key axis in tiles of 64.
+//   warp 0      TMA producer: Q, Qd once; K, Kd, V, Vd per key tile through a 2-stage ring
+//   warp 1      MMA issuer (one elected thread): S = Q K^T, Sd = Qd K^T + Q Kd^T into TMEM, then
+//               O += P V and Od' += U V + P Vd with P, U read back from TMEM as the A operand
+//   warps 2..5  softmax: one thread per query row; reads S, Sd from TMEM, keeps the running max, sum and
+//               mu, writes P = exp(s - m) and U = P o sd as 16-bit operands over the score columns
+// Od' accumulates sum(P o sd) V + sum(P) Vd; the epilogue applies Od = Od'/l - (mu/l) O, the same
+// algebra as the reference kernel (semicat/jvp_utils/ryu_triton.py:198-291).
+//
+// TMEM columns: [0,D) O, [D,2D) Od', [2D,2D+64) S / P, [2D+64,2D+128) Sd / U.  For D = 64 that is 256 columns
+// and under 100 KB of shared memory, so two CTAs share an SM and one's MMAs overlap the other's softmax.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "jvpattn_common.cuh"
+#include "sm100_ptx.cuh"
+
 namespace jvpattn {
-bool sm100_fwd_supported(const FwdArgs &) { return false; }
-cudaError_t sm100_fwd(const FwdArgs &, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;     // query rows per CTA (= TMEM lanes)
+constexpr int kBN = 64;      // keys per tile
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // in log2 units: keep the old max while p stays below 2^8
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kBoxes = D / 64;
+  alignas(1024) uint16_t q[kBoxes][kBM * 64];
+  alignas(1024) uint16_t tq[kBoxes][kBM * 64];
+  alignas(1024) uint16_t k[kStages][kBoxes][kBN * 64];
+  alignas(1024) uint16_t tk[kStages][kBoxes][kBN * 64];
+  alignas(1024) uint16_t v[kStages][kBoxes][kBN * 64];
+  alignas(1024) uint16_t tv[kStages][kBoxes][kBN * 64];
+  uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full, p_full, o_done;
+  uint32_t tmem_base;
+};
+
+struct FwdMaps {
+  CUtensorMap q, tq, k, tk, v, tv;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int D, typename T>
+__global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_constant__ FwdMaps maps, FwdArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  using Smem = FwdSmem<D>;
+  Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kBoxes = D / 64;
+  constexpr uint32_t kTmemCols = (2 * D + 128) <= 256 ? 256 : 512;
+  constexpr uint32_t kColO = 0, kColOd = D, kColS = 2 * D, kColSd = 2 * D + 64;
+  constexpr bool kBf16 = sizeof(T) == 2 && !__is_same(T, __half);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kBM;
+  const int ntiles = (a.Lk + kBN - 1) / kBN;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&s.kv_full[i], 1);
+      mbar_init(&s.kv_empty[i], 1);
+    }
+    mbar_init(&s.s_full, 1);
+    mbar_init(&s.p_full, 128);
+    mbar_init(&s.o_done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&maps.q);
+      prefetch_tensormap(&maps.k);
+      mbar_expect_tx(&s.q_full, 2 * kBM * D * 2);
+      for (int x = 0; x < kBoxes; ++x) {
+        tma_load_4d(s.q[x], &maps.q, &s.q_full, 64 * x, q0, h, b);
+        tma_load_4d(s.tq[x], &maps.tq, &s.q_full, 64 * x, q0, h, b);
+      }
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % kStages;
+        if (!mbar_wait(&s.kv_empty[st], ((j / kStages) & 1) ^ 1)) {
+          atomicExch(a.status, 101u);
+          break;
+        }
+        mbar_expect_tx(&s.kv_full[st], 4 * kBN * D * 2);
+        for (int x = 0; x < kBoxes; ++x) {
+          tma_load_4d(s.k[st][x], &maps.k, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.tk[st][x], &maps.tk, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.v[st][x], &maps.v, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.tv[st][x], &maps.tv, &s.kv_full[st], 64 * x, j * kBN, h, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kBM, kBN, kBf16, false, false);
+      constexpr uint32_t idesc_o = make_idesc(kBM, D, kBf16, false, true);
+      bool ok = mbar_wait(&s.q_full, 0);
+      if (!ok) atomicExch(a.status, 102u);
+      for (int j = 0; ok && j < ntiles; ++j) {
+        const int st = j % kStages;
+        if (!mbar_wait(&s.kv_full[st], (j / kStages) & 1)) {
+          atomicExch(a.status, 103u);
+          break;
+        }
+        tc_fence_after();
+        // S = Q K^T ; Sd = Qd K^T + Q Kd^T      (K-major operands, 16 channels per instruction)
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk & 3) * 32;
+          const uint64_t dq = make_smem_desc(smem_u32(s.q[kk >> 2]) + off, 16, 1024);
+          const uint64_t dtq = make_smem_desc(smem_u32(s.tq[kk >> 2]) + off, 16, 1024);
+          const uint64_t dk = make_smem_desc(smem_u32(s.k[st][kk >> 2]) + off, 16, 1024);
+          const uint64_t dtk = make_smem_desc(smem_u32(s.tk[st][kk >> 2]) + off, 16, 1024);
+          mma_ss(tmem + kColS, dq, dk, idesc_s, kk > 0);
+          mma_ss(tmem + kColSd, dtq, dk, idesc_s, kk > 0);
+          mma_ss(tmem + kColSd, dq, dtk, idesc_s, true);
+        }
+        tc_commit(&s.s_full);
+        if (!mbar_wait(&s.p_full, j & 1)) {
+          atomicExch(a.status, 104u);
+          break;
+        }
+        tc_fence_after();
+        // O += P V ; Od' += U V + P Vd          (A from TMEM, B = value tile read MN-major, 16 keys per instruction)
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          const uint32_t lbo = kBN * 128;  // bytes between 64-channel column blocks of a value tile
+          const uint64_t dv = make_smem_desc(smem_u32(s.v[st][0]) + kk * 2048, lbo, 1024);
+          const uint64_t dtv = make_smem_desc(smem_u32(s.tv[st][0]) + kk * 2048, lbo, 1024);
+          const bool acc = (j > 0) || (kk > 0);
+          mma_ts(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);
+          mma_ts(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, acc);
+          mma_ts(tmem + kColOd, tmem + kColS + kk * 8, dtv, idesc_o, true);
+        }
+        tc_commit(&s.kv_empty[st]);
+        tc_commit(&s.o_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warps: one thread per query row
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
+    const float sl2 = a.scale * kLog2e;
+    float m = -INFINITY, l = 0.f, mu = 0.f;
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      // tcgen05.ld / st are warp-collective: keep every decision that guards them warp-uniform
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
+        atomicExch(a.status, 105u);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sv[64];
+      {
+        uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
+        uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
+        tmem_ld32(tlane + kColS, lo);
+        tmem_ld32(tlane + kColS + 32, hi);
+        tc_wait_ld();
+      }
+      const int nvalid = a.Lk - j * kBN;  // >= 1; < 64 only on the last tile
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float t = __uint_as_float(sv[c]) * sl2;
+        t = c < nvalid ? t : -INFINITY;
+        sv[c] = __float_as_uint(t);
+        mx = fmaxf(mx, t);
+      }
+      // Keep the old reference max while the new one is at most 2^8 above it: O / Od' then need no rescale.
+      float m_new = (mx - m > kRescaleThreshold) ? mx : m;
+      if (j == 0) m_new = mx;
+      const float alpha = fast_exp2(m - m_new);  // 1 when unchanged, 0 on the first tile
+      if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
+        // S of this tile is complete, so every earlier O / Od' update has retired: safe to rescale in place.
+#pragma unroll
+        for (int c = 0; c < 2 * D; c += 32) {
+          uint32_t r[32];
+          tmem_ld32(tlane + kColO + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tlane + kColO + c, r);
+        }
+      }
+      l *= alpha;
+      mu *= alpha;
+      m = m_new;
+      float psum = 0.f, usum = 0.f;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 32) {
+        uint32_t sd[32], pk[16], uk[16];
+        tmem_ld32(tlane + kColSd + c0, sd);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(__uint_as_float(sv[c0 + 2 * i]) - m);
+          const float p1 = fast_exp2(__uint_as_float(sv[c0 + 2 * i + 1]) - m);
+          const float u0 = p0 * (__uint_as_float(sd[2 * i]) * a.scale);
+          const float u1 = p1 * (__uint_as_float(sd[2 * i + 1]) * a.scale);
+          psum += p0 + p1;
+          usum += u0 + u1;
+          pk[i] = pack2<T>(p0, p1);
+          uk[i] = pack2<T>(u0, u1);
+        }
+        // 32 score columns become 16 packed operand columns, written over columns already consumed
+        tmem_st16(tlane + kColS + c0 / 2, pk);
+        tmem_st16(tlane + kColSd + c0 / 2, uk);
+      }
+      l += psum;
+      mu += usum;
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s.p_full);
+    }
+    // ---- epilogue: O = acc / l ; Od = Od'/l - (mu/l) O ; statistics
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.o_done, (ntiles - 1) & 1))) {
+      atomicExch(a.status, 106u);
+      ok = false;
+    }
+    tc_fence_after();
+    const int qrow = q0 + row;
+    const bool live = qrow < a.Lq;  // rows past len_q take part in the collective TMEM loads but store nothing
+    if (ok) {
+      const float inv = 1.f / l;
+      const float mun = mu * inv;
+      T *op = static_cast<T *>(a.o.ptr) + a.o.offset(b, h, live ? qrow : 0);
+      T *tp = static_cast<T *>(a.to.ptr) + a.to.offset(b, h, live ? qrow : 0);
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        uint32_t ro[32], rd[32];
+        tmem_ld32(tlane + kColO + c, ro);
+        tmem_ld32(tlane + kColOd + c, rd);
+        tc_wait_ld();
+        uint32_t po[16], pd[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float o0 = __uint_as_float(ro[2 * i]) * inv, o1 = __uint_as_float(ro[2 * i + 1]) * inv;
+          const float d0 = __uint_as_float(rd[2 * i]) * inv - mun * o0;
+          const float d1 = __uint_as_float(rd[2 * i + 1]) * inv - mun * o1;
+          po[i] = pack2<T>(o0, o1);
+          pd[i] = pack2<T>(d0, d1);
+        }
+        if (live) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            reinterpret_cast<uint4 *>(op + c)[i] = make_uint4(po[4 * i], po[4 * i + 1], po[4 * i + 2], po[4 * i + 3]);
+            reinterpret_cast<uint4 *>(tp + c)[i] = make_uint4(pd[4 * i], pd[4 * i + 1], pd[4 * i + 2], pd[4 * i + 3]);
+          }
+        }
+      }
+      if (live) {
+        const size_t si = ((size_t)b * a.H + h) * a.stat_len + qrow;
+        a.lse[si] = m * kLn2 + __logf(l);
+        a.mu[si] = mun;
+        if (a.li) a.li[si] = l;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+bool view_ok(const View &v, int D) {
+  if (!v.ptr) return false;
+  if (reinterpret_cast<uintptr_t>(v.ptr) % 16 != 0) return false;
+  return v.sl % 8 == 0 && v.sh % 8 == 0 && v.sb % 8 == 0 && v.sl >= D;
+}
+
+template <int D, typename T>
+cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
+  FwdMaps maps;
+  const View *views[6] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv};
+  CUtensorMap *dst[6] = {&maps.q, &maps.tq, &maps.k, &maps.tk, &maps.v, &maps.tv};
+  for (int i = 0; i < 6; ++i) {
+    const bool is_q = i < 2;
+    if (!make_tensor_map(dst[i], views[i]->ptr, a.dtype, a.B, a.H, is_q ? a.Lq : a.Lk, D, views[i]->sb, views[i]->sh,
+                         views[i]->sl, is_q ? kBM : kBN))
+      return cudaErrorInvalidValue;
+  }
+  auto kernel = sm100_fwd_kernel<D, T>;
+  const size_t smem = sizeof(FwdSmem<D>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((a.Lq + kBM - 1) / kBM, a.H, a.B);
+  kernel<<<grid, kThreads, smem, stream>>>(maps, a);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool sm100_fwd_supported(const FwdArgs &a) {
+  if (a.D != 64 && a.D != 128) return false;
+  if (a.Lq < 1 || a.Lk < 1 || a.H > 65535 || a.B > 65535) return false;
+  const View *views[8] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv, &a.o, &a.to};
+  for (const View *v : views)
+    if (!view_ok(*v, a.D)) return false;
+  return true;
+}
+
+cudaError_t sm100_fwd(const FwdArgs &a, cudaStream_t stream) {
+  if (a.dtype == JVPATTN_BF16)
+    return a.D == 64 ? launch_fwd<64, __nv_bfloat16>(a, stream) : launch_fwd<128, __nv_bfloat16>(a, stream);
+  return a.D == 64 ? launch_fwd<64, __half>(a, stream) : launch_fwd<128, __half>(a, stream);
+}
+
+}  // namespace jvpattn
