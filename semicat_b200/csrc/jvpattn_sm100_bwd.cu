@@ -1,6 +1,515 @@
+// Attention-JVP backward for sm_100a: the VJPs of cotangents gO (on O) and G (on Od) with respect to
+// q, k, v and their tangents, from the saved row statistics (lse, mu).  tcgen05 MMAs with TMEM
+// accumulators, TMA-staged tiles, warp-specialised load / MMA / softmax-algebra roles.
+//
+// Maths (closed form of what semicat/jvp_utils/flash_jvp_backward.py:87-2290 and
+// semicat/jvp_utils/flash_attn_triton.py:406-685 compute), per (batch, head):
+//   P  = exp(scale QK^T - lse)            N = scale (Qd K^T + Q Kd^T) - mu
+//   A  = G V^T                            C = G Vd^T + gO V^T
+//   delta = rowsum(G o O)                 dsum = rowsum(G o Od) + rowsum(gO o O)
+//   W1 = scale P o (A - delta)            W2 = scale P o ((A - delta) o N + C - dsum)
+//   dQd = W1 K      dQ = W1 Kd + W2 K     dKd = W1^T Q     dK = W1^T Qd + W2^T Q
+//   dVd = P^T G     dV = (P o N)^T G + P^T gO
+// The reference gets delta / dsum from an extra L^2 pass (flash_jvp_backward.py:2012-2290); here they are
+// d-length row dot products computed by a small bandwidth-bound kernel into the caller's workspace.
+//
+// One kernel template serves both sides.  A CTA owns 128 rows of the "resident" side X and streams tiles of
+// the other side Y:
+//   query owner   X = (Q, Qd, G, gO)   Y = (K, Kd, V, Vd)     -> dQ, dQd
+//   key owner     X = (K, Kd, V, Vd)   Y = (Q, Qd, G, gO)     -> dK, dKd, dV, dVd
+// For either owner the score tiles are S = X0 Y0^T, Sd = X1 Y0^T + X0 Y1^T, A = X2 Y2^T, C = X2 Y3^T + X3 Y2^T
+// (for the key owner these are the transposes, rows = keys), and the outputs are
+//   dX1 = W1 Y0,  dX0 = W1 Y1 + W2 Y0,  and for the key owner dVd = P Y2, dV = (P o N) Y2 + P Y3.
+// The 16-bit operands P, PoN, W1, W2 are written over the fp32 score columns in TMEM and fed back to the
+// tensor core as the A operand; the Y tiles are read MN-major as the B operand.
+//
+//   warp 0      TMA producer (X once, Y through a 2-stage ring)
+//   warp 1      MMA issuer
+//   warps 2..5  one thread per owned row: score algebra, operand write-back, epilogue
 #include "jvpattn_common.cuh"
+#include "sm100_attn.cuh"
+#include "sm100_ptx.cuh"
+
 namespace jvpattn {
-bool sm100_bwd_supported(const BwdArgs &) { return false; }
-cudaError_t sm100_bwd(const BwdArgs &, cudaStream_t) { return cudaErrorNotSupported; }
-size_t sm100_bwd_workspace_bytes(int, int, int, int, int, int) { return 0; }
+namespace {
+
+using namespace ptx;
+
+constexpr int kRows = 128;
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+
+template <int D, int TILE>
+struct BwdSmem {
+  static constexpr int kBoxes = D / 64;
+  alignas(1024) uint16_t x[4][kBoxes][kRows * 64];
+  alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
+  float stats[2][4][TILE];  // key owner only: per query column lse*log2e, mu, delta, dsum (double buffered)
+  uint64_t x_full, y_full[kStages], y_empty[kStages], s_full, w_full, done;
+  uint32_t tmem_base;
+};
+
+struct BwdMaps {
+  CUtensorMap x[4], y[4];
+};
+
+struct BwdKernelArgs {
+  View out[4];            // dX0, dX1, dV, dVd (unused entries have ptr == nullptr)
+  const float *lse, *mu;  // [B, H, stat_len]
+  const float *delta, *dsum;
+  unsigned int *status;
+  int H, Lx, Ly, Lq, stat_len;  // Lx rows on the owner side, Ly on the streamed side
+  int xmask, ymask;             // which of the four X / Y tensors are loaded
+  int has_t, has_o;
+  float scale;
+};
+
+// rows of (G o O), (G o Od) + (gO o O): D/8 threads per row, 16-byte loads
+template <int D, typename T>
+__global__ void __launch_bounds__(256) row_dots_kernel(BwdArgs a, float *delta, float *dsum) {
+  constexpr int kTpr = D / 8;
+  const int64_t nrows = (int64_t)a.B * a.H * a.Lq;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = gid / kTpr;
+  const int part = (int)(gid % kTpr);
+  float d1 = 0.f, d2 = 0.f;
+  const bool live = r < nrows;
+  int b = 0, h = 0, i = 0;
+  if (live) {
+    i = (int)(r % a.Lq);
+    h = (int)((r / a.Lq) % a.H);
+    b = (int)(r / ((int64_t)a.Lq * a.H));
+    auto load8 = [&](const View &v, float (&f)[8]) {
+      const uint4 u = *reinterpret_cast<const uint4 *>(static_cast<const T *>(v.ptr) + v.offset(b, h, i) + part * 8);
+      const T *e = reinterpret_cast<const T *>(&u);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) f[t] = Elem<T>::to_f(e[t]);
+    };
+    float o[8], x[8], g[8];
+    load8(a.o, o);
+    if (a.g_to.ptr) {
+      load8(a.g_to, g);
+      load8(a.to, x);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        d1 = fmaf(g[t], o[t], d1);
+        d2 = fmaf(g[t], x[t], d2);
+      }
+    }
+    if (a.g_o.ptr) {
+      load8(a.g_o, g);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) d2 = fmaf(g[t], o[t], d2);
+    }
+  }
+#pragma unroll
+  for (int off = kTpr / 2; off > 0; off >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, off);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, off);
+  }
+  if (live && part == 0) {
+    const size_t si = ((size_t)b * a.H + h) * a.stat_len + i;
+    delta[si] = d1;
+    dsum[si] = d2;
+  }
 }
+
+template <int D, int TILE, bool kKV, bool kDoK, bool kDoV, typename T>
+__global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_constant__ BwdMaps maps, BwdKernelArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  using Smem = BwdSmem<D, TILE>;
+  Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kBoxes = D / 64;
+  constexpr int kAcc = (kDoK ? 2 : 0) + (kDoV ? 2 : 0);
+  constexpr uint32_t kColK = 0, kColKd = D;                         // dX0, dX1
+  constexpr uint32_t kColV = kDoK ? 2 * D : 0, kColVd = kColV + D;  // dV, dVd
+  constexpr uint32_t kColS = kAcc * D, kColSd = kColS + TILE, kColA = kColS + 2 * TILE, kColC = kColS + 3 * TILE;
+  constexpr uint32_t kUsed = kAcc * D + 4 * TILE;
+  static_assert(kUsed <= 512, "TMEM budget");
+  constexpr uint32_t kTmemCols = kUsed <= 256 ? 256 : 512;
+  constexpr bool kBf16 = IsBf16<T>::value;
+  constexpr uint32_t kTileBytes = TILE * D * 2;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, h = blockIdx.y, x0 = blockIdx.x * kRows;
+  const int ntiles = (a.Ly + TILE - 1) / TILE;
+  const bool has_t = a.has_t != 0, has_o = a.has_o != 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&s.x_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&s.y_full[i], 1);
+      mbar_init(&s.y_empty[i], 1);
+    }
+    mbar_init(&s.s_full, 1);
+    mbar_init(&s.w_full, 128);
+    mbar_init(&s.done, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&s.tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&maps.x[0]);
+      prefetch_tensormap(&maps.y[0]);
+      mbar_expect_tx(&s.x_full, __popc(a.xmask) * kRows * D * 2);
+      for (int t = 0; t < 4; ++t)
+        if (a.xmask >> t & 1)
+          for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[t][x], &maps.x[t], &s.x_full, 64 * x, x0, h, b);
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % kStages;
+        if (!mbar_wait(&s.y_empty[st], ((j / kStages) & 1) ^ 1)) {
+          atomicExch(a.status, 201u);
+          break;
+        }
+        mbar_expect_tx(&s.y_full[st], __popc(a.ymask) * kTileBytes);
+        for (int t = 0; t < 4; ++t)
+          if (a.ymask >> t & 1)
+            for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][t][x], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kRows, TILE, kBf16, false, false);
+      constexpr uint32_t idesc_o = make_idesc(kRows, D, kBf16, false, true);
+      // the X2 Y3^T term of C carries G Vd^T for the query owner but V gO^T for the key owner, and vice versa
+      const bool term23 = kKV ? has_o : has_t;
+      const bool term32 = kKV ? has_t : has_o;
+      bool ok = mbar_wait(&s.x_full, 0);
+      if (!ok) atomicExch(a.status, 202u);
+      bool init0 = false, init1 = false, initv = false, initvd = false;  // accumulators written at least once
+      for (int j = 0; ok && j < ntiles; ++j) {
+        const int st = j % kStages;
+        if (!mbar_wait(&s.y_full[st], (j / kStages) & 1)) {
+          atomicExch(a.status, 203u);
+          break;
+        }
+        tc_fence_after();
+        // one accumulator at a time, 16 channels per instruction
+        auto xd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.x[t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
+        auto yd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColS, xd(0, kk), yd(0, kk), idesc_s, kk > 0);
+        if (has_t) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            mma_ss(tmem + kColSd, xd(1, kk), yd(0, kk), idesc_s, kk > 0);
+            mma_ss(tmem + kColSd, xd(0, kk), yd(1, kk), idesc_s, true);
+          }
+          if (kDoK) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColA, xd(2, kk), yd(2, kk), idesc_s, kk > 0);
+          }
+        }
+        if (kDoK) {
+          bool c_started = false;
+          if (term23) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(2, kk), yd(3, kk), idesc_s, c_started || kk > 0);
+            c_started = true;
+          }
+          if (term32) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(3, kk), yd(2, kk), idesc_s, c_started || kk > 0);
+          }
+        }
+        tc_commit(&s.s_full);
+        if (!mbar_wait(&s.w_full, j & 1)) {
+          atomicExch(a.status, 204u);
+          break;
+        }
+        tc_fence_after();
+        constexpr uint32_t lbo = TILE * 128;  // bytes between 64-channel column blocks of a Y tile
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {
+          auto yb = [&](int t) { return make_smem_desc(smem_u32(s.y[st][t][0]) + kk * 2048, lbo, 1024); };
+          if (kDoK) {
+            if (has_t) {
+              mma_ts(tmem + kColKd, tmem + kColA + kk * 8, yb(0), idesc_o, init1);   // dX1 += W1 Y0
+              mma_ts(tmem + kColK, tmem + kColA + kk * 8, yb(1), idesc_o, init0);    // dX0 += W1 Y1
+              init0 = init1 = true;
+            }
+            mma_ts(tmem + kColK, tmem + kColC + kk * 8, yb(0), idesc_o, init0);      // dX0 += W2 Y0
+            init0 = true;
+          }
+          if (kDoV) {
+            if (has_t) {
+              mma_ts(tmem + kColVd, tmem + kColS + kk * 8, yb(2), idesc_o, initvd);  // dVd += P G
+              mma_ts(tmem + kColV, tmem + kColSd + kk * 8, yb(2), idesc_o, initv);   // dV  += (P o N) G
+              initv = initvd = true;
+            }
+            if (has_o) {
+              mma_ts(tmem + kColV, tmem + kColS + kk * 8, yb(3), idesc_o, initv);    // dV  += P gO
+              initv = true;
+            }
+          }
+        }
+        tc_commit(&s.y_empty[st]);
+        tc_commit(&s.done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ score algebra: one thread per owned row
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const int ctid = threadIdx.x - 64;  // 0..127 among the compute threads
+    const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
+    const float sl2 = a.scale * kLog2e;
+    const size_t stat_base = ((size_t)b * a.H + h) * a.stat_len;
+    // per-row statistics of the query owner
+    float r_lse2 = INFINITY, r_mu = 0.f, r_delta = 0.f, r_dsum = 0.f;
+    if (!kKV && x0 + row < a.Lx) {
+      r_lse2 = a.lse[stat_base + x0 + row] * kLog2e;
+      r_mu = has_t ? a.mu[stat_base + x0 + row] : 0.f;
+      r_delta = a.delta[stat_base + x0 + row];
+      r_dsum = a.dsum[stat_base + x0 + row];
+    }
+    // per-column statistics of the key owner: thread t < 4*TILE/… fetches element (t / TILE, t % TILE) of the next tile
+    auto fetch_stat = [&](int j, int e) -> float {
+      const int which = e / TILE, col = j * TILE + e % TILE;
+      if (col >= a.Lq) return which == 0 ? INFINITY : 0.f;  // padded query: P = 0
+      const size_t si = stat_base + col;
+      return which == 0 ? a.lse[si] * kLog2e : which == 1 ? (has_t ? a.mu[si] : 0.f) : which == 2 ? a.delta[si] : a.dsum[si];
+    };
+    constexpr int kStatPerThread = (4 * TILE + 127) / 128;
+    float pre[kStatPerThread];
+    if (kKV) {
+#pragma unroll
+      for (int e = 0; e < kStatPerThread; ++e) pre[e] = (ctid + 128 * e < 4 * TILE) ? fetch_stat(0, ctid + 128 * e) : 0.f;
+    }
+    bool ok = true;
+    for (int j = 0; j < ntiles; ++j) {
+      if (kKV) {
+        float *dst = &s.stats[j & 1][0][0];
+#pragma unroll
+        for (int e = 0; e < kStatPerThread; ++e)
+          if (ctid + 128 * e < 4 * TILE) dst[ctid + 128 * e] = pre[e];
+        if (j + 1 < ntiles) {
+#pragma unroll
+          for (int e = 0; e < kStatPerThread; ++e) pre[e] = (ctid + 128 * e < 4 * TILE) ? fetch_stat(j + 1, ctid + 128 * e) : 0.f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
+        atomicExch(a.status, 205u);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const float *st_lse = s.stats[j & 1][0], *st_mu = s.stats[j & 1][1];
+      const float *st_delta = s.stats[j & 1][2], *st_dsum = s.stats[j & 1][3];
+      const int nvalid = a.Ly - j * TILE;  // streamed rows in this tile (masking for the query owner)
+#pragma unroll
+      for (int c0 = 0; c0 < TILE; c0 += 32) {
+        uint32_t rs[32], ra[32];
+        float p[32], da[32];
+        tmem_ld32(tlane + kColS + c0, rs);
+        if (has_t && kDoK) tmem_ld32(tlane + kColA + c0, ra);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float lse2 = kKV ? st_lse[c0 + i] : r_lse2;
+          float pv = fast_exp2(__uint_as_float(rs[i]) * sl2 - lse2);
+          if (!kKV) pv = (c0 + i < nvalid) ? pv : 0.f;
+          p[i] = pv;
+          da[i] = (has_t && kDoK) ? __uint_as_float(ra[i]) - (kKV ? st_delta[c0 + i] : r_delta) : 0.f;
+        }
+        uint32_t rn[32];  // N = scale * sd - mu
+        if (has_t) {
+          tmem_ld32(tlane + kColSd + c0, rn);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            rn[i] = __float_as_uint(__uint_as_float(rn[i]) * a.scale - (kKV ? st_mu[c0 + i] : r_mu));
+        }
+        if (kDoV) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(p[2 * i], p[2 * i + 1]);
+          tmem_st16(tlane + kColS + c0 / 2, pk);
+          if (has_t) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack2<T>(p[2 * i] * __uint_as_float(rn[2 * i]), p[2 * i + 1] * __uint_as_float(rn[2 * i + 1]));
+            tmem_st16(tlane + kColSd + c0 / 2, pk);
+          }
+        }
+        if (kDoK) {
+          uint32_t rc[32], pk[16];
+          tmem_ld32(tlane + kColC + c0, rc);
+          tc_wait_ld();
+          if (has_t) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[i] = pack2<T>(a.scale * p[2 * i] * da[2 * i], a.scale * p[2 * i + 1] * da[2 * i + 1]);
+            tmem_st16(tlane + kColA + c0 / 2, pk);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float w[2];
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int e = 2 * i + t;
+              const float dsum = kKV ? st_dsum[c0 + e] : r_dsum;
+              const float nn = has_t ? __uint_as_float(rn[e]) : 0.f;
+              w[t] = a.scale * p[e] * (da[e] * nn + __uint_as_float(rc[e]) - dsum);
+            }
+            pk[i] = pack2<T>(w[0], w[1]);
+          }
+          tmem_st16(tlane + kColC + c0 / 2, pk);
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s.w_full);
+    }
+    // ---- epilogue: accumulators -> 16-bit outputs
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, (ntiles - 1) & 1))) {
+      atomicExch(a.status, 206u);
+      ok = false;
+    }
+    tc_fence_after();
+    if (ok) {
+      const int xr = x0 + row;
+      const bool live = xr < a.Lx;
+      auto store_acc = [&](uint32_t col, const View &v) {
+        T *dst = static_cast<T *>(v.ptr) + v.offset(b, h, live ? xr : 0);
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          uint32_t r[32], pk[16];
+          tmem_ld32(tlane + col + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          if (live) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              reinterpret_cast<uint4 *>(dst + c)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+          }
+        }
+      };
+      if (kDoK) {
+        store_acc(kColK, a.out[0]);
+        if (has_t) store_acc(kColKd, a.out[1]);
+      }
+      if (kDoV) {
+        store_acc(kColV, a.out[2]);
+        if (has_t) store_acc(kColVd, a.out[3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int D, int TILE, bool kKV, bool kDoK, bool kDoV, typename T>
+cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum, cudaStream_t stream) {
+  const bool has_t = a.g_to.ptr != nullptr, has_o = a.g_o.ptr != nullptr;
+  const View qside[4] = {a.q, a.tq, a.g_to, a.g_o};
+  const View kside[4] = {a.k, a.tk, a.v, a.tv};
+  const View *xs = kKV ? kside : qside, *ys = kKV ? qside : kside;
+  const int Lx = kKV ? a.Lk : a.Lq, Ly = kKV ? a.Lq : a.Lk;
+  // which tensors each mode reads: the tangent-side ones only with a cotangent on Od, gO only when given
+  const int qmask = 1 | (has_t ? 2 | 4 : 0) | (has_o ? 8 : 0);
+  int kmask = 1 | (has_t ? 2 | 8 : 0) | 4;
+  if (kKV && !kDoK) kmask &= 1 | 2;  // the dV / dVd pass of a split launch needs no value tiles
+  BwdMaps maps;
+  BwdKernelArgs ka{};
+  ka.xmask = kKV ? kmask : qmask;
+  ka.ymask = kKV ? qmask : kmask;
+  for (int t = 0; t < 4; ++t) {
+    if ((ka.xmask >> t & 1) &&
+        !make_tensor_map(&maps.x[t], xs[t].ptr, a.dtype, a.B, a.H, Lx, D, xs[t].sb, xs[t].sh, xs[t].sl, kRows))
+      return cudaErrorInvalidValue;
+    if ((ka.ymask >> t & 1) &&
+        !make_tensor_map(&maps.y[t], ys[t].ptr, a.dtype, a.B, a.H, Ly, D, ys[t].sb, ys[t].sh, ys[t].sl, TILE))
+      return cudaErrorInvalidValue;
+  }
+  if (kKV) {
+    ka.out[0] = a.dk; ka.out[1] = a.dtk; ka.out[2] = a.dv; ka.out[3] = a.dtv;
+  } else {
+    ka.out[0] = a.dq; ka.out[1] = a.dtq;
+  }
+  ka.lse = a.lse; ka.mu = a.mu; ka.delta = delta; ka.dsum = dsum; ka.status = a.status;
+  ka.H = a.H; ka.Lx = Lx; ka.Ly = Ly; ka.Lq = a.Lq; ka.stat_len = a.stat_len;
+  ka.has_t = has_t; ka.has_o = has_o; ka.scale = a.scale;
+  auto kernel = sm100_bwd_kernel<D, TILE, kKV, kDoK, kDoV, T>;
+  const size_t smem = sizeof(BwdSmem<D, TILE>) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  dim3 grid((Lx + kRows - 1) / kRows, a.H, a.B);
+  kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
+  count_launches(1);
+  return cudaGetLastError();
+}
+
+template <int D, typename T>
+cudaError_t launch_bwd(const BwdArgs &a, cudaStream_t stream) {
+  float *delta = static_cast<float *>(a.workspace);
+  float *dsum = delta + (size_t)a.B * a.H * a.stat_len;
+  {
+    constexpr int kTpr = D / 8;
+    const int64_t threads = (int64_t)a.B * a.H * a.Lq * kTpr;
+    row_dots_kernel<D, T><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, delta, dsum);
+    count_launches(1);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  cudaError_t e = cudaSuccess;
+  if constexpr (D == 64) {
+    e = launch_side<D, 64, false, true, false, T>(a, delta, dsum, stream);
+    if (e != cudaSuccess) return e;
+    return launch_side<D, 64, true, true, true, T>(a, delta, dsum, stream);
+  } else {
+  // head_dim 128: four fp32 accumulators of 128 columns do not fit TMEM next to the score tiles, so the
+  // key side runs as two passes (dK, dKd | dV, dVd) over 32-row query tiles
+  e = launch_side<D, 32, false, true, false, T>(a, delta, dsum, stream);
+  if (e != cudaSuccess) return e;
+  e = launch_side<D, 32, true, true, false, T>(a, delta, dsum, stream);
+  if (e != cudaSuccess) return e;
+  return launch_side<D, 32, true, false, true, T>(a, delta, dsum, stream);
+  }
+}
+
+}  // namespace
+
+size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_len) {
+  (void)Lq; (void)Lk; (void)D;
+  size_t bytes = (size_t)2 * B * H * stat_len * sizeof(float);
+  return (bytes + 255) / 256 * 256;
+}
+
+bool sm100_bwd_supported(const BwdArgs &a) {
+  if (a.D != 64 && a.D != 128) return false;
+  if (a.Lq < 1 || a.Lk < 1 || a.H > 65535 || a.B > 65535) return false;
+  const bool has_t = a.g_to.ptr != nullptr, has_o = a.g_o.ptr != nullptr;
+  const View *always[] = {&a.q, &a.k, &a.v, &a.o, &a.dq, &a.dk, &a.dv};
+  for (const View *v : always)
+    if (!tma_view_ok(*v, a.D)) return false;
+  if (has_t) {
+    const View *t[] = {&a.tq, &a.tk, &a.tv, &a.to, &a.g_to, &a.dtq, &a.dtk, &a.dtv};
+    for (const View *v : t)
+      if (!tma_view_ok(*v, a.D)) return false;
+  }
+  if (has_o && !tma_view_ok(a.g_o, a.D)) return false;
+  return true;
+}
+
+cudaError_t sm100_bwd(const BwdArgs &a, cudaStream_t stream) {
+  if (a.dtype == JVPATTN_BF16)
+    return a.D == 64 ? launch_bwd<64, __nv_bfloat16>(a, stream) : launch_bwd<128, __nv_bfloat16>(a, stream);
+  return a.D == 64 ? launch_bwd<64, __half>(a, stream) : launch_bwd<128, __half>(a, stream);
+}
+
+}  // namespace jvpattn

@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 
 #include "jvpattn_common.cuh"
+#include "sm100_attn.cuh"
 #include "sm100_ptx.cuh"
 
 namespace jvpattn {
@@ -27,8 +28,6 @@ constexpr int kBM = 128;     // query rows per CTA (= TMEM lanes)
 constexpr int kBN = 64;      // keys per tile
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr float kLog2e = 1.4426950408889634f;
-constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units: keep the old max while p stays below 2^8
 
 template <int D>
@@ -48,25 +47,6 @@ struct FwdMaps {
   CUtensorMap q, tq, k, tk, v, tv;
 };
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-template <typename T>
-__device__ __forceinline__ uint32_t pack2(float a, float b);
-template <>
-__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t *>(&h);
-}
-template <>
-__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t *>(&h);
-}
-
 template <int D, typename T>
 __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_constant__ FwdMaps maps, FwdArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -75,7 +55,7 @@ __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_consta
   constexpr int kBoxes = D / 64;
   constexpr uint32_t kTmemCols = (2 * D + 128) <= 256 ? 256 : 512;
   constexpr uint32_t kColO = 0, kColOd = D, kColS = 2 * D, kColSd = 2 * D + 64;
-  constexpr bool kBf16 = sizeof(T) == 2 && !__is_same(T, __half);
+  constexpr bool kBf16 = IsBf16<T>::value;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kBM;
@@ -140,17 +120,16 @@ __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_consta
           break;
         }
         tc_fence_after();
-        // S = Q K^T ; Sd = Qd K^T + Q Kd^T      (K-major operands, 16 channels per instruction)
+        // S = Q K^T ; Sd = Qd K^T + Q Kd^T      (K-major operands, 16 channels per instruction; one
+        // accumulator at a time)
+        auto kdesc = [&](const uint16_t *tile, int kk) { return make_smem_desc(smem_u32(tile) + (kk & 3) * 32, 16, 1024); };
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          mma_ss(tmem + kColS, kdesc(s.q[kk >> 2], kk), kdesc(s.k[st][kk >> 2], kk), idesc_s, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk & 3) * 32;
-          const uint64_t dq = make_smem_desc(smem_u32(s.q[kk >> 2]) + off, 16, 1024);
-          const uint64_t dtq = make_smem_desc(smem_u32(s.tq[kk >> 2]) + off, 16, 1024);
-          const uint64_t dk = make_smem_desc(smem_u32(s.k[st][kk >> 2]) + off, 16, 1024);
-          const uint64_t dtk = make_smem_desc(smem_u32(s.tk[st][kk >> 2]) + off, 16, 1024);
-          mma_ss(tmem + kColS, dq, dk, idesc_s, kk > 0);
-          mma_ss(tmem + kColSd, dtq, dk, idesc_s, kk > 0);
-          mma_ss(tmem + kColSd, dq, dtk, idesc_s, true);
+          mma_ss(tmem + kColSd, kdesc(s.tq[kk >> 2], kk), kdesc(s.k[st][kk >> 2], kk), idesc_s, kk > 0);
+          mma_ss(tmem + kColSd, kdesc(s.q[kk >> 2], kk), kdesc(s.tk[st][kk >> 2], kk), idesc_s, true);
         }
         tc_commit(&s.s_full);
         if (!mbar_wait(&s.p_full, j & 1)) {
@@ -302,12 +281,6 @@ __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_consta
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-bool view_ok(const View &v, int D) {
-  if (!v.ptr) return false;
-  if (reinterpret_cast<uintptr_t>(v.ptr) % 16 != 0) return false;
-  return v.sl % 8 == 0 && v.sh % 8 == 0 && v.sb % 8 == 0 && v.sl >= D;
-}
-
 template <int D, typename T>
 cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
   FwdMaps maps;
@@ -336,7 +309,7 @@ bool sm100_fwd_supported(const FwdArgs &a) {
   if (a.Lq < 1 || a.Lk < 1 || a.H > 65535 || a.B > 65535) return false;
   const View *views[8] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv, &a.o, &a.to};
   for (const View *v : views)
-    if (!view_ok(*v, a.D)) return false;
+    if (!tma_view_ok(*v, a.D)) return false;
   return true;
 }
 
