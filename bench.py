@@ -1,0 +1,411 @@
+#!/usr/bin/env python
+"""Benchmark of the JVP-attention hot path: fused forward + backward TFLOP/s on synthetic data.
+
+    python bench.py --gpus N --steps K --warmup W            # this library on N GPUs of one node
+    python bench.py --impl reference --steps K --warmup W     # the CPU path on the host cores
+
+Workload (BASELINE config 2): bf16, non-causal, B=64, H=12, L=128, d=64; q ~ N(0,1)/sqrt(d), k, v ~ N(0,1),
+tangents ~ 0.1 N(0,1), cotangents on O and Od ~ N(0,1); tensors are (B,H,L,D) views of (B,S,H,D) memory,
+the layout the denoiser hands over.  One step = one forward (O, Od, lse, mu) + one backward (all six
+VJPs, both cotangents) over one batch.  With N > 1 every rank runs that batch on its own GPU (the
+(batch, head) problems are independent: no data-path collective, weak scaling).
+
+FLOP model: GEMM-unit = 2 L^2 d per head; forward 6 units, backward 15, total 42 B H L^2 d per step.
+Recomputation inside the kernels is not counted.  Byte model: T = 2 B H L d; forward 8T, backward 16T.
+
+One JSON line is printed by rank 0; see the keys at the bottom of `main`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, H, L, D, value distribution)
+    "config2": dict(B=64, H=12, L=128, D=64, q_scale=None, t_scale=0.1),
+    "L2048_d64": dict(B=32, H=16, L=2048, D=64, q_scale=1.0, t_scale=1.0),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def flops_per_step(B, H, L, D):
+    return 42.0 * B * H * L * L * D
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    except Exception:
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+# ----------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while a region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------------------------- inputs
+def host_inputs(cfg, seed):
+    import torch
+    B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
+    g = torch.Generator().manual_seed(seed)
+    qs = 1.0 / math.sqrt(D) if cfg["q_scale"] is None else cfg["q_scale"]
+    # generated directly in the model's (B,S,H,D) memory order
+    mk = lambda s: (torch.randn(B, L, H, D, generator=g) * s).to(torch.bfloat16)
+    t = cfg["t_scale"]
+    return {"q": mk(qs), "k": mk(1.0), "v": mk(1.0), "tq": mk(t), "tk": mk(t), "tv": mk(t), "g_o": mk(1.0), "g_to": mk(1.0)}
+
+
+class DeviceSet:
+    """One resident set of inputs, outputs and gradients plus its pre-marshalled launch plan."""
+
+    def __init__(self, host, device):
+        import torch
+        from semicat_b200 import ops
+        self.t = {n: x.to(device).transpose(1, 2) for n, x in host.items()}  # (B,H,L,D) views
+        q = self.t["q"]
+        B, H, L, D = q.shape
+        like = lambda: torch.empty(B, L, H, D, dtype=q.dtype, device=device).transpose(1, 2)
+        self.o, self.to = like(), like()
+        self.lse = torch.empty(B, H, ops.stat_len(L), dtype=torch.float32, device=device)
+        self.mu = torch.empty_like(self.lse)
+        self.grads = [like() for _ in range(6)]
+        t = self.t
+        self.plan = ops.Plan(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], self.o, self.to, self.lse, self.mu,
+                             g_o=t["g_o"], g_to=t["g_to"], grads=self.grads)
+
+    def step(self):
+        self.plan.forward()
+        self.plan.backward()
+
+    def nbytes(self):
+        return sum(x.numel() * x.element_size() for x in (*self.t.values(), self.o, self.to, *self.grads))
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+def run_device(cfg, sets, steps, warmup, dist, sampler):
+    """Device-resident timing: CUDA events on the launching stream around exactly `steps` steps."""
+    import torch
+    from semicat_b200 import _lib
+    count0 = _lib.launch_count()
+    for i in range(max(warmup, 3)):
+        sets[i % len(sets)].step()
+    torch.cuda.synchronize()
+    per_step = (_lib.launch_count() - count0) // max(warmup, 3)  # kernels of this library per step
+    graphs, mode = [], "eager"
+    try:  # one CUDA graph per input set: the steps are launch-bound at this size
+        for s in sets:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                s.step()
+            graphs.append(g)
+        mode = "cuda_graph"
+        for g in graphs:
+            g.replay()
+        torch.cuda.synchronize()
+    except Exception as e:  # pragma: no cover - depends on the driver
+        print(f"[bench] CUDA graph capture unavailable ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
+        graphs, mode = [], "eager"
+        torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    launches0 = _lib.launch_count()
+    with sampler:
+        start.record()
+        for i in range(steps):
+            if graphs:
+                graphs[i % len(graphs)].replay()
+            else:
+                sets[i % len(sets)].step()
+        end.record()
+        end.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    launched = (_lib.launch_count() - launches0) if not graphs else per_step * steps
+    return ms, launched, mode
+
+
+def run_profile(sets, steps):
+    """Per-kernel device time from CUDA events recorded by the library around each launch."""
+    import torch
+    from semicat_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.profile_begin()
+    for i in range(steps):
+        sets[i % len(sets)].step()
+    return _lib.profile_end()
+
+
+def run_e2e(cfg, host_sets, steps, warmup, device, dist, sampler):
+    """End to end through the public API with HOST buffers: per step, pinned host -> device copies of the
+    eight inputs, sdpa_jvp under torch.func.jvp, reverse mode for both cotangents, and the eight results
+    copied back to pinned host memory."""
+    import torch
+    from semicat_b200 import sdpa_jvp
+    pinned = [{n: x.pin_memory() for n, x in hs.items()} for hs in host_sets]
+    B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
+    out_host = [torch.empty(B, H, L, D, dtype=torch.bfloat16).pin_memory() for _ in range(8)]
+    names = ("q", "k", "v", "tq", "tk", "tv")
+
+    def step(i):
+        src = pinned[i % len(pinned)]
+        dev = {n: x.to(device, non_blocking=True) for n, x in src.items()}
+        leaves = [dev[n].transpose(1, 2).requires_grad_(True) for n in names]
+        o, to = torch.func.jvp(sdpa_jvp, tuple(leaves[:3]), tuple(leaves[3:]))
+        grads = torch.autograd.grad([o, to], leaves, [dev["g_o"].transpose(1, 2), dev["g_to"].transpose(1, 2)])
+        for dst, src_t in zip(out_host, (o.detach(), to.detach(), *grads)):
+            dst.copy_(src_t, non_blocking=True)
+
+    for i in range(max(warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        t0 = time.perf_counter()
+        start.record()
+        for i in range(steps):
+            step(i)
+        end.record()
+        end.synchronize()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+    if dist is not None:
+        dist.barrier()
+    ms = max(start.elapsed_time(end), wall_ms)  # device time and host wall agree unless the host is the bottleneck
+    per_tensor = B * H * L * D * 2
+    return ms, 8 * per_tensor, 8 * per_tensor
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+def cpu_path(cfg, repeats, threads=None):
+    """The CPU path of the reference (math attention under torch.func.jvp, differentiated by autograd),
+    restated in oracle/torch_cpu_path.py, timed on the host cores over the full workload in fp32."""
+    from oracle import torch_cpu_path
+    best, used = torch_cpu_path.time_fwd_bwd(cfg["B"], cfg["H"], cfg["L"], cfg["D"], repeats=repeats, threads=threads)
+    return best, used
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="config2", choices=list(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    flops = flops_per_step(B, H, L, D)
+    config = {"workload": f"{args.workload}: JVP attention fwd+bwd, bf16, non-causal, B{B} H{H} L{L} d{D}, "
+                          "both cotangents, (B,S,H,D) memory layout",
+              "flop_model": "42*B*H*L^2*d per step (6 fwd + 15 bwd GEMM-units)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        import torch
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        from oracle import torch_cpu_path
+        for _ in range(min(args.warmup, 2)):
+            torch_cpu_path.time_fwd_bwd(B, H, L, D, repeats=1, threads=cores)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            torch_cpu_path.time_fwd_bwd(B, H, L, D, repeats=1, threads=cores)
+        ms = (time.perf_counter() - t0) * 1e3 / max(args.steps, 1)
+        val = flops / (ms * 1e-3) / 1e12
+        config["l2"] = "n/a (host)"
+        print(json.dumps({
+            "impl": "reference", "metric": "jvp_attn_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": 0,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                             "sample": "the full workload per step, fp32, torch math attention under torch.func.jvp + autograd"},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }))
+        return
+
+    import torch
+    from semicat_b200 import _lib
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product has no CPU path (use --impl reference for the CPU arm)")
+    _lib.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=device)
+        dist = dist_mod
+
+    # rotate over enough resident input sets that consecutive steps never find their data in the 126 MB L2
+    host_sets = [host_inputs(cfg, seed=1000 * rank + i) for i in range(4)]
+    sets = [DeviceSet(hs, device) for hs in host_sets]
+    resident_mb = sum(s.nbytes() for s in sets) / 1e6
+    while resident_mb < 400 and len(sets) < 16:
+        host_sets.append(host_inputs(cfg, seed=1000 * rank + len(sets)))
+        sets.append(DeviceSet(host_sets[-1], device))
+        resident_mb = sum(s.nbytes() for s in sets) / 1e6
+    config["l2"] = f"rotating over {len(sets)} resident input/output sets ({resident_mb:.0f} MB) > 126 MB L2"
+
+    sampler = ClockSampler(local_rank)
+    ms, launched, mode = run_device(cfg, sets, args.steps, args.warmup, dist, sampler)
+    config["launch"] = mode
+    e2e_steps = max(3, min(args.steps, 20))
+    e2e_ms, h2d, d2h = run_e2e(cfg, host_sets, e2e_steps, min(args.warmup, 3), device, dist, sampler)
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    ms_per_step = ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    e2e_value = world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12
+
+    line = {
+        "metric": "jvp_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps, "api": "sdpa_jvp under torch.func.jvp + torch.autograd.grad, pinned host buffers"},
+        "gpu_launches": int(launched),
+    }
+
+    if rank == 0:
+        pk = peaks()
+        T = 2.0 * B * H * L * D
+        stat = 4.0 * B * H * L
+        # algorithmic bytes / FLOPs of each kernel: the tensors it must read and write once
+        model = {
+            "sm100_fwd_kernel": (8 * T + 2 * stat, 6),
+            "row_dots_kernel": (4 * T + 2 * stat, 0),
+            "sm100_bwd_kernel<query owner>": (10 * T + 4 * stat, 9),
+            "sm100_bwd_kernel<key owner>": (12 * T + 4 * stat, 12),
+        }
+        with sampler:
+            prof = run_profile(sets, max(8, min(args.steps, 40)))
+        total = sum(v[0] for v in prof.values()) or 1.0
+        unit_flops = 2.0 * B * H * L * L * D
+        kernels = []
+        for name, (tot_ms, n) in sorted(prof.items(), key=lambda kv: -kv[1][0]):
+            by, units = model.get(name, (0.0, 0))
+            avg = tot_ms / n
+            kernels.append({"kernel": name, "launches": n, "avg_ms": avg, "share": tot_ms / total,
+                            "gb_s": by / (avg * 1e-3) / 1e9, "executed_tflops": units * unit_flops / (avg * 1e-3) / 1e12})
+        line["kernels"] = kernels
+        intensity = flops / (24 * T)
+        bound = "hbm" if intensity < pk["bf16_tflops"] * 1e12 / (pk["hbm_gbs"] * 1e9) else "tensor"
+        top = kernels[0]
+        if bound == "hbm":
+            line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gb_s"], "peak": pk["hbm_gbs"],
+                                "unit": "GB/s", "frac": top["gb_s"] / pk["hbm_gbs"], "traffic": None,
+                                "peak_source": pk["source"]}
+        else:
+            line["roofline"] = {"bound": "tensor", "kernel": top["kernel"], "achieved": top["executed_tflops"],
+                                "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": top["executed_tflops"] / pk["bf16_tflops"],
+                                "traffic": None, "peak_source": pk["source"]}
+        # whole-step view against the binding ceiling: max(FLOPs / tensor peak, bytes / HBM peak)
+        t_roof = max(flops / (pk["bf16_tflops"] * 1e12), (24 * T + 6 * stat) / (pk["hbm_gbs"] * 1e9))
+        line["step_roofline"] = {"t_roof_ms": t_roof * 1e3, "frac_of_t_roof": t_roof * 1e3 / ms_per_step,
+                                 "frac_of_bf16_peak": value / world / pk["bf16_tflops"]}
+        if not args.no_extras and world == 1:
+            del sets, host_sets
+            torch.cuda.empty_cache()
+            big = WORKLOADS["L2048_d64"]
+            bsets = [DeviceSet(host_inputs(big, seed=7 + i), device) for i in range(2)]
+            with sampler:
+                bms, _, _ = run_device(big, bsets, 6, 3, None, ClockSampler(local_rank))
+                bprof = run_profile(bsets, 4)
+            bf = flops_per_step(big["B"], big["H"], big["L"], big["D"])
+            tf = bf / (bms / 6 * 1e-3) / 1e12
+            line["long_sequence"] = {"workload": "B32 H16 L2048 d64 bf16, N(0,1) primals and tangents", "ms_per_step": bms / 6,
+                                     "tflops": tf, "frac_of_bf16_peak": tf / pk["bf16_tflops"],
+                                     "kernel_ms": {k_: v_[0] / v_[1] for k_, v_ in bprof.items()}}
+            del bsets
+            cpu_s, cores = cpu_path(cfg, repeats=3)
+            line["cpu_baseline"] = {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": "the full config-2 workload, fp32, best of 3 "
+                                              f"({cpu_s * 1e3:.0f} ms per fwd+bwd)"}
+        line["clocks"] = sampler.summary()
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -106,6 +106,15 @@ int jvpattn_selected_kernels(const jvpattn_problem *p, int which);
 /* Number of kernels this library has launched in the calling process (all threads). */
 uint64_t jvpattn_launch_count(void);
 
+/* Optional per-kernel timing for measurement harnesses (no counterpart in the reference, which relies on
+ * triton.testing.do_bench around whole calls, ryu_triton.py:958-1007).  Between _begin and _end every
+ * launch is bracketed by CUDA events on its stream; _end synchronises the device and returns, per kernel
+ * id in [0, JVPATTN_NUM_KERNELS), the summed device time in milliseconds and the launch count. */
+#define JVPATTN_NUM_KERNELS 7
+int jvpattn_profile_begin(void);
+int jvpattn_profile_end(double *total_ms, uint64_t *launches);
+const char *jvpattn_kernel_name(int id);
+
 /* Synchronises the current device and returns the device-side status word: 0 if no bounded wait has
  * run out since the last call, else a code identifying the wait that gave up.  Clears the word. */
 int jvpattn_device_status(void);

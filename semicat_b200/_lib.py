@@ -28,8 +28,9 @@ KERNELS_AUTO, KERNELS_SIMT, KERNELS_TCGEN05 = 0, 1, 2
 EXPORTS = (
     "jvpattn_fwd", "jvpattn_bwd", "jvpattn_bwd_workspace_bytes", "jvpattn_selected_kernels",
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
-    "jvpattn_abi_version",
+    "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
 )
+NUM_KERNELS = 7
 
 
 class Tensor4(ctypes.Structure):
@@ -120,6 +121,12 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_last_cuda_error.restype = ctypes.c_char_p
         lib.jvpattn_abi_version.argtypes = []
         lib.jvpattn_abi_version.restype = ctypes.c_int
+        lib.jvpattn_profile_begin.argtypes = []
+        lib.jvpattn_profile_begin.restype = ctypes.c_int
+        lib.jvpattn_profile_end.argtypes = [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_uint64)]
+        lib.jvpattn_profile_end.restype = ctypes.c_int
+        lib.jvpattn_kernel_name.argtypes = [ctypes.c_int]
+        lib.jvpattn_kernel_name.restype = ctypes.c_char_p
         if lib.jvpattn_abi_version() != 1:
             raise RuntimeError("libjvpattn.so ABI version mismatch; rebuild it")
         _lib = lib
@@ -142,3 +149,16 @@ def launch_count() -> int:
 
 def device_status() -> int:
     return int(load().jvpattn_device_status())
+
+
+def profile_begin() -> None:
+    check(load().jvpattn_profile_begin(), "jvpattn_profile_begin")
+
+
+def profile_end() -> dict:
+    """Stop per-kernel timing; returns {kernel name: (total_ms, launches)} for kernels that ran."""
+    lib = load()
+    ms = (ctypes.c_double * NUM_KERNELS)()
+    n = (ctypes.c_uint64 * NUM_KERNELS)()
+    check(lib.jvpattn_profile_end(ms, n), "jvpattn_profile_end")
+    return {lib.jvpattn_kernel_name(i).decode(): (float(ms[i]), int(n[i])) for i in range(NUM_KERNELS) if n[i]}

@@ -5,13 +5,43 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 #include "jvpattn_common.cuh"
 
 namespace jvpattn {
 
 static std::atomic<uint64_t> g_launches{0};
-void count_launches(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// ---- optional per-kernel timing (off by default; used by bench.py for the roofline figures)
+struct ProfSlot {
+  int id;
+  cudaEvent_t start, stop;
+};
+static std::atomic<bool> g_profiling{false};
+static std::mutex g_prof_mutex;
+static std::vector<ProfSlot *> g_prof_slots;
+
+LaunchScope::LaunchScope(int id, cudaStream_t stream) : id_(id), stream_(stream), slot_(nullptr) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!g_profiling.load(std::memory_order_relaxed)) return;
+  ProfSlot *slot = new ProfSlot{id, nullptr, nullptr};
+  if (cudaEventCreate(&slot->start) != cudaSuccess || cudaEventCreate(&slot->stop) != cudaSuccess) {
+    (void)cudaGetLastError();
+    delete slot;
+    return;
+  }
+  cudaEventRecord(slot->start, stream);
+  slot_ = slot;
+}
+
+LaunchScope::~LaunchScope() {
+  if (!slot_) return;
+  ProfSlot *slot = static_cast<ProfSlot *>(slot_);
+  cudaEventRecord(slot->stop, stream_);
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_prof_slots.push_back(slot);
+}
 
 // Written by a kernel whose bounded wait ran out; read and cleared by jvpattn_device_status().
 __device__ unsigned int g_status_word = 0;
@@ -190,6 +220,50 @@ const char *jvpattn_strerror(int code) {
     case JVPATTN_ELAUNCH: return "CUDA launch failed (see jvpattn_last_cuda_error)";
     case JVPATTN_EDEVICE: return "a bounded device-side wait ran out";
     default: return "unknown jvpattn error code";
+  }
+}
+
+int jvpattn_profile_begin(void) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  g_profiling.store(true);
+  return JVPATTN_OK;
+}
+
+int jvpattn_profile_end(double *total_ms, uint64_t *launches) {
+  g_profiling.store(false);
+  cudaError_t e = cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  for (int i = 0; i < JVPATTN_NUM_KERNELS; ++i) {
+    if (total_ms) total_ms[i] = 0.0;
+    if (launches) launches[i] = 0;
+  }
+  for (ProfSlot *slot : g_prof_slots) {
+    float ms = 0.f;
+    if (e == cudaSuccess && cudaEventElapsedTime(&ms, slot->start, slot->stop) == cudaSuccess && slot->id >= 0 &&
+        slot->id < JVPATTN_NUM_KERNELS) {
+      if (total_ms) total_ms[slot->id] += ms;
+      if (launches) launches[slot->id] += 1;
+    }
+    cudaEventDestroy(slot->start);
+    cudaEventDestroy(slot->stop);
+    delete slot;
+  }
+  g_prof_slots.clear();
+  (void)cudaGetLastError();
+  return e == cudaSuccess ? JVPATTN_OK : note_cuda(e);
+}
+
+const char *jvpattn_kernel_name(int id) {
+  static_assert(kNumKernelIds == JVPATTN_NUM_KERNELS, "kernel id table");
+  switch (id) {
+    case kIdFwdTc: return "sm100_fwd_kernel";
+    case kIdRowDots: return "row_dots_kernel";
+    case kIdBwdQueryTc: return "sm100_bwd_kernel<query owner>";
+    case kIdBwdKeyTc: return "sm100_bwd_kernel<key owner>";
+    case kIdFwdSimt: return "simt_fwd_kernel";
+    case kIdBwdQuerySimt: return "simt_bwd_q_kernel";
+    case kIdBwdKeySimt: return "simt_bwd_kv_kernel";
+    default: return "?";
   }
 }
 

@@ -52,7 +52,20 @@ cudaError_t sm100_fwd(const FwdArgs &a, cudaStream_t stream);
 cudaError_t sm100_bwd(const BwdArgs &a, cudaStream_t stream);
 size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_len);
 
-void count_launches(int n);
+// Kernel identifiers used by the launch counter and the optional per-kernel event timing.
+enum KernelId {
+  kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kNumKernelIds
+};
+
+// Brackets one kernel launch: counts it and, while profiling is on, records a CUDA event before and
+// after it on the launching stream.
+struct LaunchScope {
+  LaunchScope(int id, cudaStream_t stream);
+  ~LaunchScope();
+  int id_;
+  cudaStream_t stream_;
+  void *slot_;
+};
 
 template <typename T> struct Elem;
 template <> struct Elem<__nv_bfloat16> {

@@ -395,11 +395,13 @@ __global__ void __launch_bounds__(kWarps * 32) simt_bwd_kv_kernel(BwdArgs a) {
 }
 
 template <typename K, typename A>
-cudaError_t launch(K kernel, dim3 grid, size_t smem, const A &a, cudaStream_t stream) {
+cudaError_t launch(int id, K kernel, dim3 grid, size_t smem, const A &a, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kernel<<<grid, kWarps * 32, smem, stream>>>(a);
-  count_launches(1);
+  {
+    LaunchScope scope(id, stream);
+    kernel<<<grid, kWarps * 32, smem, stream>>>(a);
+  }
   return cudaGetLastError();
 }
 
@@ -410,8 +412,8 @@ cudaError_t simt_fwd(const FwdArgs &a, cudaStream_t stream) {
   size_t esz = 2;
   size_t smem = 4 * kTile * (a.D + 2) * esz + (size_t)kWarps * kRowsPerWarp * 2 * a.D * sizeof(float);
   dim3 grid((a.Lq + kRows - 1) / kRows, a.H, a.B);
-  return a.dtype == JVPATTN_BF16 ? launch(simt_fwd_kernel<__nv_bfloat16>, grid, smem, a, stream)
-                                 : launch(simt_fwd_kernel<__half>, grid, smem, a, stream);
+  return a.dtype == JVPATTN_BF16 ? launch(kIdFwdSimt, simt_fwd_kernel<__nv_bfloat16>, grid, smem, a, stream)
+                                 : launch(kIdFwdSimt, simt_fwd_kernel<__half>, grid, smem, a, stream);
 }
 
 cudaError_t simt_bwd(const BwdArgs &a, cudaStream_t stream) {
@@ -422,15 +424,15 @@ cudaError_t simt_bwd(const BwdArgs &a, cudaStream_t stream) {
   cudaError_t e = cudaSuccess;
   if (a.Lq > 0) {
     dim3 grid((a.Lq + kRows - 1) / kRows, a.H, a.B);
-    e = a.dtype == JVPATTN_BF16 ? launch(simt_bwd_q_kernel<__nv_bfloat16>, grid, tile + rows, a, stream)
-                                : launch(simt_bwd_q_kernel<__half>, grid, tile + rows, a, stream);
+    e = a.dtype == JVPATTN_BF16 ? launch(kIdBwdQuerySimt, simt_bwd_q_kernel<__nv_bfloat16>, grid, tile + rows, a, stream)
+                                : launch(kIdBwdQuerySimt, simt_bwd_q_kernel<__half>, grid, tile + rows, a, stream);
     if (e != cudaSuccess) return e;
   }
   if (a.Lk > 0) {
     dim3 grid((a.Lk + kRows - 1) / kRows, a.H, a.B);
     size_t smem = tile + 5 * kTile * sizeof(float) + rows;
-    e = a.dtype == JVPATTN_BF16 ? launch(simt_bwd_kv_kernel<__nv_bfloat16>, grid, smem, a, stream)
-                                : launch(simt_bwd_kv_kernel<__half>, grid, smem, a, stream);
+    e = a.dtype == JVPATTN_BF16 ? launch(kIdBwdKeySimt, simt_bwd_kv_kernel<__nv_bfloat16>, grid, smem, a, stream)
+                                : launch(kIdBwdKeySimt, simt_bwd_kv_kernel<__half>, grid, smem, a, stream);
   }
   return e;
 }

@@ -449,8 +449,10 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid((Lx + kRows - 1) / kRows, a.H, a.B);
-  kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
-  count_launches(1);
+  {
+    LaunchScope scope(kKV ? kIdBwdKeyTc : kIdBwdQueryTc, stream);
+    kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
+  }
   return cudaGetLastError();
 }
 
@@ -461,8 +463,10 @@ cudaError_t launch_bwd(const BwdArgs &a, cudaStream_t stream) {
   {
     constexpr int kTpr = D / 8;
     const int64_t threads = (int64_t)a.B * a.H * a.Lq * kTpr;
-    row_dots_kernel<D, T><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, delta, dsum);
-    count_launches(1);
+    {
+      LaunchScope scope(kIdRowDots, stream);
+      row_dots_kernel<D, T><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, delta, dsum);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }

@@ -297,8 +297,10 @@ cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   dim3 grid((a.Lq + kBM - 1) / kBM, a.H, a.B);
-  kernel<<<grid, kThreads, smem, stream>>>(maps, a);
-  count_launches(1);
+  {
+    LaunchScope scope(kIdFwdTc, stream);
+    kernel<<<grid, kThreads, smem, stream>>>(maps, a);
+  }
   return cudaGetLastError();
 }
 

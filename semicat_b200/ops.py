@@ -134,6 +134,42 @@ def jvp_attention_bwd(q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv
     return workspace
 
 
+class Plan:
+    """Pre-marshalled forward + backward on fixed tensors: everything ctypes needs is built once, so a
+    launch costs two foreign calls.  The tensors (all (B, H, L, D) views) must stay alive and in place.
+    Used where the same buffers are run repeatedly (benchmarks, CUDA-graph capture)."""
+
+    def __init__(self, q, k, v, tq, tk, tv, o, to, lse, mu, g_o=None, g_to=None, grads=None, scale=None,
+                 kernels=KERNELS_AUTO):
+        self.lib = _lib.load()
+        self.device = q.device
+        self.keep = [q, k, v, tq, tk, tv, o, to, lse, mu, g_o, g_to, grads]
+        dt, dev = q.dtype, q.device
+        self.prob = _problem(q, k, lse.shape[-1], scale, kernels)
+        byref = lambda t, n: ctypes.byref(self._hold(_t4(t, n, dt, dev))) if t is not None else None
+        self._structs = []
+        ins = [byref(t, n) for n, t in zip("q k v tq tk tv o to".split(), (q, k, v, tq, tk, tv, o, to))]
+        self.fwd_args = [ctypes.byref(self.prob), *ins, lse.data_ptr(), mu.data_ptr(), None]
+        self.bwd_args = None
+        if grads is not None:
+            with _on_device(dev):
+                need = int(self.lib.jvpattn_bwd_workspace_bytes(ctypes.byref(self.prob)))
+            self.workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+            outs = [byref(t, n) for n, t in zip("dq dk dv dtq dtk dtv".split(), grads)]
+            self.bwd_args = [ctypes.byref(self.prob), *ins, byref(g_o, "g_o"), byref(g_to, "g_to"),
+                             lse.data_ptr(), mu.data_ptr(), *outs, self.workspace.data_ptr(), self.workspace.numel()]
+
+    def _hold(self, struct):
+        self._structs.append(struct)
+        return struct
+
+    def forward(self):
+        _lib.check(self.lib.jvpattn_fwd(*self.fwd_args, torch.cuda.current_stream(self.device).cuda_stream), "jvpattn_fwd")
+
+    def backward(self):
+        _lib.check(self.lib.jvpattn_bwd(*self.bwd_args, torch.cuda.current_stream(self.device).cuda_stream), "jvpattn_bwd")
+
+
 def selected_kernels(B, H, Lq, Lk, D, dtype=torch.bfloat16, which="fwd") -> int:
     prob = Problem(B, H, Lq, Lk, D, stat_len(Lq), _DTYPES[dtype], KERNELS_AUTO, 0.0)
     return int(_lib.load().jvpattn_selected_kernels(ctypes.byref(prob), 0 if which == "fwd" else 1))
