@@ -41,7 +41,8 @@ enum {
   JVPATTN_EWORKSPACE = -6,/* workspace NULL or smaller than jvpattn_bwd_workspace_bytes()     */
   JVPATTN_EARCH = -7,     /* no CUDA device, or the device is not sm_100                      */
   JVPATTN_ELAUNCH = -8,   /* the CUDA runtime refused a launch; see jvpattn_last_cuda_error() */
-  JVPATTN_EDEVICE = -9    /* a bounded device-side wait ran out; see jvpattn_device_status()  */
+  JVPATTN_EDEVICE = -9,   /* a bounded device-side wait ran out; see jvpattn_device_status()  */
+  JVPATTN_ETOOLARGE = -10 /* jvpattn_bwd_static: problem larger than the built-in scratch     */
 };
 
 enum { JVPATTN_BF16 = 0, JVPATTN_FP16 = 1 };
@@ -98,6 +99,24 @@ int jvpattn_bwd(const jvpattn_problem *p,
                 const jvpattn_tensor *dq, const jvpattn_tensor *dk, const jvpattn_tensor *dv,
                 const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
                 void *workspace, size_t workspace_bytes, void *stream);
+
+/* Same backward for callers that have no way to allocate device memory (no counterpart in the reference,
+ * whose wrappers allocate freely through torch).  Takes no workspace: the scratch lives in a fixed
+ * 2 MiB array inside the library image, present on every GPU that loads the library until the process
+ * exits.  Limit: batch * heads * stat_len <= JVPATTN_STATIC_SCRATCH_ROWS, otherwise JVPATTN_ETOOLARGE
+ * and nothing is launched.  The call itself allocates nothing.  The first call on each device resolves
+ * the array's device address (cudaGetSymbolAddress) and should come before any stream capture.  All calls
+ * on a device share the array: calls that overlap on the GPU race and must be ordered by the caller. */
+#define JVPATTN_STATIC_SCRATCH_ROWS 262144
+int jvpattn_bwd_static(const jvpattn_problem *p,
+                       const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                       const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                       const jvpattn_tensor *o, const jvpattn_tensor *to,
+                       const jvpattn_tensor *g_o, const jvpattn_tensor *g_to,
+                       const float *lse, const float *mu,
+                       const jvpattn_tensor *dq, const jvpattn_tensor *dk, const jvpattn_tensor *dv,
+                       const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
+                       void *stream);
 
 /* Which kernel family AUTO resolves to for this problem (JVPATTN_KERNELS_SIMT or _TCGEN05), for the
  * forward (which = 0) or the backward (which = 1); negative error code for an invalid problem. */

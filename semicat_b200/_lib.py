@@ -29,7 +29,9 @@ EXPORTS = (
     "jvpattn_fwd", "jvpattn_bwd", "jvpattn_bwd_workspace_bytes", "jvpattn_selected_kernels",
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
+    "jvpattn_bwd_static",
 )
+STATIC_SCRATCH_ROWS = 262144
 NUM_KERNELS = 7
 
 
@@ -107,6 +109,8 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_fwd.restype = ctypes.c_int
         lib.jvpattn_bwd.argtypes = [P] + [T] * 10 + [F, F] + [T] * 6 + [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         lib.jvpattn_bwd.restype = ctypes.c_int
+        lib.jvpattn_bwd_static.argtypes = [P] + [T] * 10 + [F, F] + [T] * 6 + [ctypes.c_void_p]
+        lib.jvpattn_bwd_static.restype = ctypes.c_int
         lib.jvpattn_bwd_workspace_bytes.argtypes = [P]
         lib.jvpattn_bwd_workspace_bytes.restype = ctypes.c_size_t
         lib.jvpattn_selected_kernels.argtypes = [P, ctypes.c_int]

@@ -219,6 +219,7 @@ const char *jvpattn_strerror(int code) {
     case JVPATTN_EARCH: return "no usable CUDA device: this library runs on sm_100 (B200) only and has no CPU path";
     case JVPATTN_ELAUNCH: return "CUDA launch failed (see jvpattn_last_cuda_error)";
     case JVPATTN_EDEVICE: return "a bounded device-side wait ran out";
+    case JVPATTN_ETOOLARGE: return "problem exceeds the built-in scratch of jvpattn_bwd_static (batch*heads*stat_len > JVPATTN_STATIC_SCRATCH_ROWS); use jvpattn_bwd with a caller workspace";
     default: return "unknown jvpattn error code";
   }
 }
@@ -344,6 +345,73 @@ int jvpattn_bwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn
   bool fast = p->kernels != JVPATTN_KERNELS_SIMT && sm100_bwd_supported(a);
   if (p->kernels == JVPATTN_KERNELS_TCGEN05 && !fast) return JVPATTN_EINVAL;
   return note_cuda(fast ? sm100_bwd(a, s) : simt_bwd(a, s));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no allocator to offer: a plug-in that only receives tensor pointers
+// from its framework, a process whose memory pool has already claimed all of HBM, or a code region where
+// calling cudaMalloc (or the framework's caching allocator) is forbidden.  jvpattn_bwd asks such a caller
+// for a workspace it cannot produce.  This variant keeps the scratch (the two fp32 row-dot vectors,
+// 2 * batch * heads * stat_len floats) in a fixed array inside the library image instead.
+//
+// The array lives in every CUDA context that loads the library (2 MiB per GPU, until the process exits).
+// Host code cannot use the symbol's name as a pointer: the address is resolved per device with
+// cudaGetSymbolAddress the first time the entry point is called with that device current, and cached.
+// That first call therefore does set-up work beyond enqueueing kernels and should be made before any
+// stream capture is started.
+//
+// All calls on a device share the one array and it keeps whatever the previous call left there.  Nothing
+// in it has to start at zero (the row-dot kernel overwrites every element the later kernels read), but
+// two calls that overlap on the GPU (different streams, no ordering between them) race on it; order them.
+static __device__ __align__(256) float g_static_scratch[2 * JVPATTN_STATIC_SCRATCH_ROWS];
+
+namespace {
+struct StaticScratchSlot {
+  int state = 0;  // 0 not resolved, 1 resolved, -1 failed
+  void *ptr = nullptr;
+};
+StaticScratchSlot g_static_slots[kMaxDevices];
+std::mutex g_static_mutex;
+}  // namespace
+
+int jvpattn_bwd_static(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
+                       const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
+                       const jvpattn_tensor *o, const jvpattn_tensor *to, const jvpattn_tensor *g_o,
+                       const jvpattn_tensor *g_to, const float *lse, const float *mu, const jvpattn_tensor *dq,
+                       const jvpattn_tensor *dk, const jvpattn_tensor *dv, const jvpattn_tensor *dtq,
+                       const jvpattn_tensor *dtk, const jvpattn_tensor *dtv, void *stream) {
+  JVP_TRY(check_problem(p));
+  const int64_t rows = (int64_t)p->batch * p->heads * p->stat_len;
+  if (rows > JVPATTN_STATIC_SCRATCH_ROWS) return JVPATTN_ETOOLARGE;
+  if (jvpattn_bwd_workspace_bytes(p) > sizeof(float) * 2 * JVPATTN_STATIC_SCRATCH_ROWS) return JVPATTN_ETOOLARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    note_cuda(e);
+    return JVPATTN_EARCH;
+  }
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratchSlot &slot = g_static_slots[dev];
+    if (slot.state == 0) {
+      void *ptr = nullptr;
+      e = cudaGetSymbolAddress(&ptr, g_static_scratch);  // device address of the array in THIS device's context
+      if (e != cudaSuccess || ptr == nullptr) {
+        note_cuda(e);
+        slot.state = -1;
+      } else {
+        slot.ptr = ptr;
+        slot.state = 1;
+      }
+    }
+    if (slot.state != 1) return JVPATTN_EARCH;
+    scratch = slot.ptr;
+  }
+  return jvpattn_bwd(p, q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv, dtq, dtk, dtv, scratch,
+                     sizeof(float) * 2 * JVPATTN_STATIC_SCRATCH_ROWS, stream);
 }
 
 }  // extern "C"

@@ -134,6 +134,29 @@ def jvp_attention_bwd(q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv
     return workspace
 
 
+def jvp_attention_bwd_static(q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv, dtq=None, dtk=None, dtv=None,
+                             scale=None, kernels=KERNELS_AUTO):
+    """Backward through ``jvpattn_bwd_static``: same results as :func:`jvp_attention_bwd`, but the scratch
+    comes from a fixed 2 MiB array inside the library, so neither this wrapper nor the library allocates
+    device memory.  For hosts that cannot allocate (all memory pre-claimed by their own pool, or no access to
+    an allocator at the point of the call).  Limit: ``B * H * stat_len <= _lib.STATIC_SCRATCH_ROWS``; larger
+    problems raise ``JvpAttnError`` (code -10).  Calls on one device share the array, so do not let two of
+    them overlap on different streams; make the first call on a device outside any stream capture."""
+    lib = _lib.load()
+    _check_shapes(q, k, [("tq", tq), ("o", o), ("to", to), ("g_o", g_o), ("g_to", g_to), ("dq", dq), ("dtq", dtq)],
+                  [("k", k), ("v", v), ("tk", tk), ("tv", tv), ("dk", dk), ("dv", dv), ("dtk", dtk), ("dtv", dtv)])
+    prob = _problem(q, k, lse.shape[-1], scale, kernels)
+    dev, dt = q.device, q.dtype
+    names = ("q", "k", "v", "tq", "tk", "tv", "o", "to", "g_o", "g_to", "dq", "dk", "dv", "dtq", "dtk", "dtv")
+    structs = [_t4(t, n, dt, dev) for n, t in zip(names, (q, k, v, tq, tk, tv, o, to, g_o, g_to, dq, dk, dv, dtq, dtk, dtv))]
+    ref = lambda a: ctypes.byref(a) if a is not None else None
+    with _on_device(dev):
+        rc = lib.jvpattn_bwd_static(ctypes.byref(prob), *[ref(a) for a in structs[:10]],
+                                    lse.data_ptr(), mu.data_ptr() if mu is not None else None,
+                                    *[ref(a) for a in structs[10:]], torch.cuda.current_stream(dev).cuda_stream)
+    _lib.check(rc, "jvpattn_bwd_static")
+
+
 class Plan:
     """Pre-marshalled forward + backward on fixed tensors: everything ctypes needs is built once, so a
     launch costs two foreign calls.  The tensors (all (B, H, L, D) views) must stay alive and in place.
