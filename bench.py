@@ -148,7 +148,7 @@ class DeviceSet:
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
-def run_device(cfg, sets, steps, warmup, dist, sampler):
+def run_device(cfg, sets, steps, warmup, dist, sampler, use_graph=True):
     """Device-resident timing: CUDA events on the launching stream around exactly `steps` steps."""
     import torch
     from semicat_b200 import _lib
@@ -159,6 +159,8 @@ def run_device(cfg, sets, steps, warmup, dist, sampler):
     per_step = (_lib.launch_count() - count0) // max(warmup, 3)  # kernels of this library per step
     graphs, mode = [], "eager"
     try:  # one CUDA graph per input set: the steps are launch-bound at this size
+        if not use_graph:
+            raise RuntimeError("disabled by --profile-mode")
         for s in sets:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -263,6 +265,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="config2", choices=list(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
+    ap.add_argument("--profile-mode", action="store_true",
+                    help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
@@ -324,10 +328,14 @@ def main():
     config["l2"] = f"rotating over {len(sets)} resident input/output sets ({resident_mb:.0f} MB) > 126 MB L2"
 
     sampler = ClockSampler(local_rank)
-    ms, launched, mode = run_device(cfg, sets, args.steps, args.warmup, dist, sampler)
+    ms, launched, mode = run_device(cfg, sets, args.steps, args.warmup, dist, sampler, use_graph=not args.profile_mode)
     config["launch"] = mode
     e2e_steps = max(3, min(args.steps, 20))
-    e2e_ms, h2d, d2h = run_e2e(cfg, host_sets, e2e_steps, min(args.warmup, 3), device, dist, sampler)
+    if args.profile_mode:
+        args.no_extras = True
+        e2e_ms, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_ms, h2d, d2h = run_e2e(cfg, host_sets, e2e_steps, min(args.warmup, 3), device, dist, sampler)
     if dist is not None:
         t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
