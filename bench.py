@@ -248,6 +248,68 @@ def run_e2e(cfg, host_sets, steps, warmup, device, dist, sampler):
     return ms, 8 * per_tensor, 8 * per_tensor
 
 
+# ----------------------------------------------------------------------------------------------- DiT training
+TRAIN_CONFIGS = {
+    # BASELINE configs 3 and 4: 12 layers, hidden 768, 12 heads (d = 64), MLP 3072, adaLN, bf16 autocast
+    "dit_lm1b": dict(vocab=30522, length=128, global_batch=512, embed="naive"),
+    "dit_text8": dict(vocab=27, length=256, global_batch=256, embed="rms"),
+}
+
+
+def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp"):
+    """Flow-map training steps of the DiT (semicat_b200/train_step.py) on uniform random tokens: global batch
+    sharded over the ranks, forward-mode JVP through every attention layer for the first `sd_prop` of each
+    shard, AdamW, one flat gradient all-reduce per step.  Returns (ms per step, tokens per step, last loss)."""
+    import torch
+    from semicat_b200 import ddp, train_step
+    tc = TRAIN_CONFIGS[name]
+    torch.manual_seed(1234)  # same initial weights on every rank
+    net = train_step.DiT(tc["vocab"], 768, 128, 12, 12, dropout=0.1, length=tc["length"], embed_type=tc["embed"]).to(device)
+    flat = ddp.FlatGradients(net.parameters())
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True)
+    lo, hi = ddp.shard_bounds(tc["global_batch"], rank, world)
+    gen = torch.Generator().manual_seed(99 + rank)
+    host_tokens = [torch.randint(0, tc["vocab"], (hi - lo, tc["length"]), generator=gen).pin_memory() for _ in range(4)]
+    dgen = torch.Generator(device=device).manual_seed(7 + rank)
+    loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+
+    def step(i):
+        x1 = host_tokens[i % 4].to(device, non_blocking=True)
+        noise = train_step.draw_noise(x1, tc["vocab"], generator=dgen)
+        flat.zero()
+        vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention)
+        loss = train_step.total_loss(vf, sd)
+        loss.backward()
+        flat.all_reduce_mean()
+        opt.step()
+        loss_host.copy_(loss.detach(), non_blocking=True)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        start.record()
+        for i in range(steps):
+            step(i)
+        end.record()
+        end.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = start.elapsed_time(end) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    peak_gb = torch.cuda.max_memory_allocated() / 1e9
+    del net, opt, flat
+    torch.cuda.empty_cache()
+    return ms, tc["global_batch"] * tc["length"], float(loss_host), peak_gb
+
+
 # ----------------------------------------------------------------------------------------------- CPU arm
 def cpu_path(cfg, repeats, threads=None):
     """The CPU path of the reference (math attention under torch.func.jvp, differentiated by autograd),
@@ -263,11 +325,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="config2", choices=list(WORKLOADS))
+    ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS))
+    ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
     args = ap.parse_args()
+    if args.workload in TRAIN_CONFIGS:
+        return main_train(args)
     cfg = WORKLOADS[args.workload]
     B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
     rank = int(os.environ.get("RANK", "0"))
@@ -408,8 +473,55 @@ def main():
             line["cpu_baseline"] = {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": "the full config-2 workload, fp32, best of 3 "
                                               f"({cpu_s * 1e3:.0f} ms per fwd+bwd)"}
+    if not args.no_extras:
+        # DiT flow-map training (BASELINE config 3) at the same N: fixed global batch 512, sharded over the ranks
+        try:
+            sets = host_sets = None  # release the attention buffers before the model is built
+            torch.cuda.empty_cache()
+            tms, tokens, tloss, peak_gb = run_train("dit_lm1b", 3, 2, device, rank, world, dist, sampler, sd_prop=0.25)
+            line["train"] = {"workload": "DiT 12x768, 12 heads, vocab 30522, seq 128, global batch 512, sd_prop 0.25 (lag), "
+                                         "bf16 autocast, AdamW, uniform random tokens", "scaling": "strong",
+                             "ms_per_step": tms, "tokens_per_s": tokens / (tms * 1e-3), "steps": 3, "loss": tloss,
+                             "peak_mem_gb": peak_gb}
+        except Exception as e:  # the attention line above stands on its own
+            line["train"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if rank == 0:
         line["clocks"] = sampler.summary()
         print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main_train(args):
+    """`--workload dit_lm1b | dit_text8`: the training step is the benchmark step; metric = tokens/s."""
+    import torch
+    from semicat_b200 import _lib, ddp
+    _lib.load()
+    rank, world, local_rank = ddp.init_from_env("nccl")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    import torch.distributed as dist_mod
+    dist = dist_mod if world > 1 else None
+    sampler = ClockSampler(local_rank)
+    launches0 = _lib.launch_count()
+    ms, tokens, loss, peak_gb = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist, sampler,
+                                          sd_prop=args.sd_prop)
+    launched = _lib.launch_count() - launches0
+    tc = TRAIN_CONFIGS[args.workload]
+    if rank == 0:
+        val = tokens / (ms * 1e-3)
+        print(json.dumps({
+            "metric": "dit_jvp_train_tokens_per_s", "value": val, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: DiT 12x768/12 heads, vocab {tc['vocab']}, seq {tc['length']}, global batch "
+                                   f"{tc['global_batch']}, sd_prop {args.sd_prop} (lag), AdamW", "parallelism": f"dp{world}",
+                       "l2": "activations per step far exceed the 126 MB L2"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 8 // world, "d2h_bytes_per_step": 4,
+                    "note": "token ids come from pinned host memory and the loss goes back to the host every step"},
+            "gpu_launches": int(launched), "loss": loss, "peak_mem_gb": peak_gb, "clocks": sampler.summary(),
+        }))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

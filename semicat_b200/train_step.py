@@ -1,0 +1,203 @@
+"""The caller of the hot path, restated for measurement: the adaLN DiT denoiser and the flow-map training
+step that pushes ``torch.func.jvp`` through it.
+
+This is NOT part of the kernel library; it exists so that ``bench.py`` can report DiT JVP-training
+tokens/s on the reference's architecture without the reference checkout (which does not travel to the
+GPU box) and without Lightning/Hydra.  Architecture and objective follow the reference:
+
+* denoiser: semicat/net/duo.py:299-360 (``DIT``), blocks :101-166 (LayerNorm, adaLN modulation with
+  zero-initialised projection, bias-free qkv, rotary on q and k in fp32, attention through
+  ``safe_sdpa_jvp`` when ``jvp_attention`` else ``F.scaled_dot_product_attention``, 4x GELU-tanh MLP, gates),
+  timestep embedders :69-93 on ``s`` and ``t - s``, dense (B, L, V) input embedding :169-180 / :205-296,
+  zero-initialised adaLN output layer :183-202;
+* objective: semicat/models/semicat.py:169-191 (``model_step``: the first ``sd_prop`` of the batch takes the
+  self-distillation step, the rest the cross-entropy step), :89-110 (VFM step), :112-167 (``lag``
+  self-distillation: ``torch.func.jvp`` of the flow map x_{s,t} with respect to t, squared error against
+  a no-grad target), :210-229 (flow map), :70-85 (interpolation towards the one-hot token).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .functional import safe_sdpa_jvp
+
+
+def _rotate(x, cos, sin):
+    """Non-interleaved rotary embedding on (B, S, H, D); cos/sin are (S, D/2) fp32, so the result is fp32
+    (the reference's q and k reach the attention in fp32 under bf16 autocast for the same reason)."""
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    cos, sin = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.cat((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
+
+
+class TimeEmbed(nn.Module):
+    def __init__(self, dim, n_freq=256, max_period=10000):
+        super().__init__()
+        self.mlp = nn.Sequential(nn.Linear(n_freq, dim), nn.SiLU(), nn.Linear(dim, dim))
+        half = n_freq // 2
+        self.register_buffer("freqs", torch.exp(-math.log(max_period) * torch.arange(half) / half))
+
+    def forward(self, t):
+        a = t[:, None] * self.freqs[None]
+        return self.mlp(torch.cat((a.cos(), a.sin()), dim=-1))
+
+
+class Block(nn.Module):
+    def __init__(self, dim, heads, cond_dim, dropout):
+        super().__init__()
+        self.heads, self.dim = heads, dim
+        self.norm1, self.norm2 = nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.attn_qkv = nn.Linear(dim, 3 * dim, bias=False)
+        self.attn_out = nn.Linear(dim, dim, bias=False)
+        self.mlp = nn.Sequential(nn.Linear(dim, 4 * dim), nn.GELU(approximate="tanh"), nn.Linear(4 * dim, dim))
+        self.drop = nn.Dropout(dropout)
+        self.ada = nn.Linear(cond_dim, 6 * dim)
+        nn.init.zeros_(self.ada.weight)
+        nn.init.zeros_(self.ada.bias)
+
+    def forward(self, x, cos, sin, c, attention):
+        B, S, _ = x.shape
+        sh1, sc1, g1, sh2, sc2, g2 = self.ada(c)[:, None].chunk(6, dim=2)
+        h = self.norm1(x) * (1.0 + sc1) + sh1
+        q, k, v = self.attn_qkv(h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
+        q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
+        if attention == "jvp":
+            a = safe_sdpa_jvp(q, k, v)
+        elif attention == "math":  # plain formula: supports forward-mode AD anywhere (used by the CPU tests)
+            qh, kh, vh = (z.transpose(1, 2).float() for z in (q, k, v))
+            w = torch.softmax(qh @ kh.transpose(-1, -2) / math.sqrt(qh.shape[-1]), dim=-1)
+            a = (w @ vh).transpose(1, 2).to(x.dtype)
+        else:
+            a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2).to(q.dtype)).transpose(1, 2)
+        x = self.drop(self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)) * g1) + x
+        return self.drop(self.mlp(self.norm2(x) * (1.0 + sc2) + sh2) * g2) + x
+
+
+class RmsEmbed(nn.Module):
+    """duo.py:205-296: RMS time scaling, projection, small residual MLP, FiLM on the condition, RMSNorm."""
+
+    def __init__(self, vocab, dim, cond_dim, residual_scale=0.1, eps=1e-6):
+        super().__init__()
+        self.vocab, self.eps, self.res = vocab, eps, residual_scale
+        self.proj = nn.Linear(vocab, dim)
+        self.mlp = nn.Sequential(nn.Linear(dim, 2 * dim), nn.GELU(approximate="tanh"), nn.Linear(2 * dim, dim))
+        self.gamma, self.beta = nn.Linear(cond_dim, dim), nn.Linear(cond_dim, dim)
+        self.norm = nn.RMSNorm(dim, eps=1e-8)
+        for lin in (self.gamma, self.beta):
+            nn.init.zeros_(lin.weight)
+            nn.init.zeros_(lin.bias)
+
+    def forward(self, x, t, cond):
+        scale = torch.rsqrt(t ** 2 + (1.0 - t) ** 2 * self.vocab + self.eps).view(-1, 1, 1)
+        h = self.proj(x * scale)
+        h = h + self.res * self.mlp(h)
+        return self.norm((1.0 + self.gamma(cond).unsqueeze(1)) * h + self.beta(cond).unsqueeze(1))
+
+
+class NaiveEmbed(nn.Module):
+    def __init__(self, vocab, dim):
+        super().__init__()
+        self.seq = nn.Linear(vocab, dim)
+        self.coeff = vocab ** 0.5
+
+    def forward(self, x, t, cond):
+        return self.seq(x / self.coeff)
+
+
+class DiT(nn.Module):
+    def __init__(self, vocab_size, hidden_size=768, cond_dim=128, n_blocks=12, n_heads=12, dropout=0.1, length=128,
+                 embed_type="naive"):
+        super().__init__()
+        self.embed = NaiveEmbed(vocab_size, hidden_size) if embed_type == "naive" else RmsEmbed(vocab_size, hidden_size, cond_dim)
+        self.s_map, self.t_map = TimeEmbed(cond_dim), TimeEmbed(cond_dim)
+        d = hidden_size // n_heads
+        ang = torch.arange(length)[:, None] * (1.0 / (10000 ** (torch.arange(0, d, 2) / d)))[None]
+        self.register_buffer("cos", ang.cos())
+        self.register_buffer("sin", ang.sin())
+        self.blocks = nn.ModuleList(Block(hidden_size, n_heads, cond_dim, dropout) for _ in range(n_blocks))
+        self.norm_out = nn.LayerNorm(hidden_size)
+        self.ada_out = nn.Linear(cond_dim, 2 * hidden_size)
+        self.head = nn.Linear(hidden_size, vocab_size)
+        for lin in (self.ada_out, self.head):
+            nn.init.zeros_(lin.weight)
+            nn.init.zeros_(lin.bias)
+
+    def forward(self, x, s, t, attention="sdpa"):
+        cond = F.silu(self.s_map(s)) + F.silu(self.t_map(t - s))
+        h = self.embed(x, s, cond)
+        for blk in self.blocks:
+            h = blk(h, self.cos, self.sin, cond, attention)
+        shift, scale = self.ada_out(cond)[:, None].chunk(2, dim=2)
+        return self.head(self.norm_out(h) * (1.0 + scale) + shift)
+
+
+def randomise_zero_init(net: nn.Module, std=0.05, seed=0):
+    """A freshly built DiT multiplies its attention branch by zero gates; parity tests un-zero them first."""
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for p in net.parameters():
+            if p.numel() and not p.any():
+                p.copy_(torch.randn(p.shape, generator=g).to(p) * std)
+
+
+def interpolate(x0, x1, t):
+    """(1 - t) x0 + t onehot(x1) without materialising the one-hot (semicat.py:70-85)."""
+    xt = x0 * (1.0 - t)
+    xt.scatter_add_(-1, x1[..., None], t.expand_as(xt[..., :1]).to(xt.dtype))
+    return xt
+
+
+def flow_map(net, x, s, t, attention):
+    dt = (t - s) / (1.0 - s + 1e-8)
+    diff = net(x, s, t, attention=attention).softmax(dim=-1) - x
+    return x + dt.view(-1, 1, 1) * diff
+
+
+def draw_noise(x1, vocab, generator=None):
+    """The random draws of one step, separated out so that tests can inject the same draws everywhere."""
+    B = x1.shape[0]
+    dev = x1.device
+    return {"x0": torch.randn(B, x1.shape[1], vocab, device=dev, generator=generator),
+            "t_vfm": torch.rand(B, device=dev, generator=generator), "t_sd": torch.rand(B, device=dev, generator=generator),
+            "u_sd": torch.rand(B, device=dev, generator=generator)}
+
+
+def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0):
+    """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L)."""
+    B = x1.shape[0]
+    split = int(sd_prop * B)
+    dev_type = x1.device.type
+    ac = lambda: torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None)
+    x0 = noise["x0"]
+    # VFM step on the tail of the batch
+    vf_loss = None
+    if split < B:
+        t = noise["t_vfm"][split:]
+        xt = interpolate(x0[split:], x1[split:], t.view(-1, 1, 1))
+        with ac():
+            pred = net(xt, t, t)
+        vf_loss = F.cross_entropy(pred.float().transpose(-1, 1), x1[split:], label_smoothing=label_smoothing)
+    if split == 0:
+        return vf_loss, None
+    # self-distillation ("lag") step on the head of the batch: d/dt of the flow map by forward-mode AD
+    t = noise["t_sd"][:split]
+    s = noise["u_sd"][:split] * t
+    xs = interpolate(x0[:split], x1[:split], s.view(-1, 1, 1))
+    with ac():
+        xst, dv = torch.func.jvp(lambda _t: flow_map(net, xs, s, _t, jvp_attention), (t,), (torch.ones_like(t),))
+        xst = xst.detach()
+        with torch.no_grad():
+            target = net(xst, t, t).softmax(dim=-1)
+    sd_loss = ((1.0 - t).view(-1, 1, 1) * dv - target + xst).pow(2).sum(dim=-1).mean()
+    return vf_loss, sd_loss
+
+
+def total_loss(vf_loss, sd_loss):
+    if vf_loss is None:
+        return sd_loss
+    return vf_loss if sd_loss is None else vf_loss + sd_loss
