@@ -34,6 +34,9 @@ WORKLOADS = {
     # name: (B, H, L, D, value distribution)
     "config2": dict(B=64, H=12, L=128, D=64, q_scale=None, t_scale=0.1),
     "L2048_d64": dict(B=32, H=16, L=2048, D=64, q_scale=1.0, t_scale=1.0),
+    # a slice of the long-sequence sweep small enough for an ncu capture (268 MB resident per set)
+    "L2048_d64_small": dict(B=4, H=16, L=2048, D=64, q_scale=1.0, t_scale=1.0),
+    "L2048_d128_small": dict(B=2, H=16, L=2048, D=128, q_scale=1.0, t_scale=1.0),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 

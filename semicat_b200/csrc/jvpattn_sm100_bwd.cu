@@ -25,7 +25,8 @@
 //
 //   warp 0      TMA producer (X once, Y through a 2-stage ring)
 //   warp 1      MMA issuer
-//   warps 2..5  one thread per owned row: score algebra, operand write-back, epilogue
+//   warps 2..9  two threads per owned row (each on half of the tile's columns): score algebra, operand
+//               write-back over consumed score columns, epilogue
 #include "jvpattn_common.cuh"
 #include "sm100_attn.cuh"
 #include "sm100_ptx.cuh"
@@ -37,14 +38,15 @@ using namespace ptx;
 
 constexpr int kRows = 128;
 constexpr int kStages = 2;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // TMA warp, MMA warp, 8 score-algebra warps
+constexpr int kComputeThreads = 256;
 
 template <int D, int TILE>
 struct BwdSmem {
   static constexpr int kBoxes = D / 64;
   alignas(1024) uint16_t x[4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
-  float stats[2][4][TILE];  // key owner only: per query column lse*log2e, mu, delta, dsum (double buffered)
+  float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
   uint64_t x_full, y_full[kStages], y_empty[kStages], s_full, w_full, done;
   uint32_t tmem_base;
 };
@@ -142,7 +144,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       mbar_init(&s.y_empty[i], 1);
     }
     mbar_init(&s.s_full, 1);
-    mbar_init(&s.w_full, 128);
+    mbar_init(&s.w_full, kComputeThreads);
     mbar_init(&s.done, 1);
     fence_barrier_init();
   }
@@ -232,23 +234,27 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {
           auto yb = [&](int t) { return make_smem_desc(smem_u32(s.y[st][t][0]) + kk * 2048, lbo, 1024); };
+          // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the
+          // start of its own column range (see the score-algebra warps)
+          constexpr int CH = TILE / 2;
+          const uint32_t oa = ((16 * kk) / CH) * CH + ((16 * kk) % CH) / 2;
           if (kDoK) {
             if (has_t) {
-              mma_ts(tmem + kColKd, tmem + kColA + kk * 8, yb(0), idesc_o, init1);   // dX1 += W1 Y0
-              mma_ts(tmem + kColK, tmem + kColA + kk * 8, yb(1), idesc_o, init0);    // dX0 += W1 Y1
+              mma_ts(tmem + kColKd, tmem + kColA + oa, yb(0), idesc_o, init1);   // dX1 += W1 Y0
+              mma_ts(tmem + kColK, tmem + kColA + oa, yb(1), idesc_o, init0);    // dX0 += W1 Y1
               init0 = init1 = true;
             }
-            mma_ts(tmem + kColK, tmem + kColC + kk * 8, yb(0), idesc_o, init0);      // dX0 += W2 Y0
+            mma_ts(tmem + kColK, tmem + kColC + oa, yb(0), idesc_o, init0);      // dX0 += W2 Y0
             init0 = true;
           }
           if (kDoV) {
             if (has_t) {
-              mma_ts(tmem + kColVd, tmem + kColS + kk * 8, yb(2), idesc_o, initvd);  // dVd += P G
-              mma_ts(tmem + kColV, tmem + kColSd + kk * 8, yb(2), idesc_o, initv);   // dV  += (P o N) G
+              mma_ts(tmem + kColVd, tmem + kColS + oa, yb(2), idesc_o, initvd);  // dVd += P G
+              mma_ts(tmem + kColV, tmem + kColSd + oa, yb(2), idesc_o, initv);   // dV  += (P o N) G
               initv = initvd = true;
             }
             if (has_o) {
-              mma_ts(tmem + kColV, tmem + kColS + kk * 8, yb(3), idesc_o, initv);    // dV  += P gO
+              mma_ts(tmem + kColV, tmem + kColS + oa, yb(3), idesc_o, initv);    // dV  += P gO
               initv = true;
             }
           }
@@ -258,121 +264,115 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------------ score algebra: one thread per owned row
+    // ------------------------------------------------------------------ score algebra: two threads per owned row
+    constexpr int CH = TILE / 2;  // score columns per thread and tile
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int ctid = threadIdx.x - 64;  // 0..127 among the compute threads
+    const int col0 = half * CH;
+    const int ctid = threadIdx.x - 64;  // 0..255 among the compute threads
     const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
     const float sl2 = a.scale * kLog2e;
+    const float2 sl2x2 = make_float2(sl2, sl2), scx2 = make_float2(a.scale, a.scale);
     const size_t stat_base = ((size_t)b * a.H + h) * a.stat_len;
-    // per-row statistics of the query owner
-    float r_lse2 = INFINITY, r_mu = 0.f, r_delta = 0.f, r_dsum = 0.f;
+    // per-row statistics of the query owner: {lse * log2e, mu, delta, dsum}
+    float4 rstat = make_float4(INFINITY, 0.f, 0.f, 0.f);
     if (!kKV && x0 + row < a.Lx) {
-      r_lse2 = a.lse[stat_base + x0 + row] * kLog2e;
-      r_mu = has_t ? a.mu[stat_base + x0 + row] : 0.f;
-      r_delta = a.delta[stat_base + x0 + row];
-      r_dsum = a.dsum[stat_base + x0 + row];
+      rstat.x = a.lse[stat_base + x0 + row] * kLog2e;
+      rstat.y = has_t ? a.mu[stat_base + x0 + row] : 0.f;
+      rstat.z = a.delta[stat_base + x0 + row];
+      rstat.w = a.dsum[stat_base + x0 + row];
     }
-    // per-column statistics of the key owner: thread t < 4*TILE/… fetches element (t / TILE, t % TILE) of the next tile
-    auto fetch_stat = [&](int j, int e) -> float {
-      const int which = e / TILE, col = j * TILE + e % TILE;
-      if (col >= a.Lq) return which == 0 ? INFINITY : 0.f;  // padded query: P = 0
+    // per-column statistics of the key owner: the first TILE compute threads fetch one query column each,
+    // one tile ahead, and publish it through shared memory
+    auto fetch_stat = [&](int j) -> float4 {
+      const int col = j * TILE + ctid;
+      if (ctid >= TILE || col >= a.Lq) return make_float4(INFINITY, 0.f, 0.f, 0.f);  // padded query: P = 0
       const size_t si = stat_base + col;
-      return which == 0 ? a.lse[si] * kLog2e : which == 1 ? (has_t ? a.mu[si] : 0.f) : which == 2 ? a.delta[si] : a.dsum[si];
+      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
     };
-    constexpr int kStatPerThread = (4 * TILE + 127) / 128;
-    float pre[kStatPerThread];
-    if (kKV) {
-#pragma unroll
-      for (int e = 0; e < kStatPerThread; ++e) pre[e] = (ctid + 128 * e < 4 * TILE) ? fetch_stat(0, ctid + 128 * e) : 0.f;
-    }
+    float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kKV) pre = fetch_stat(0);
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       if (kKV) {
-        float *dst = &s.stats[j & 1][0][0];
-#pragma unroll
-        for (int e = 0; e < kStatPerThread; ++e)
-          if (ctid + 128 * e < 4 * TILE) dst[ctid + 128 * e] = pre[e];
-        if (j + 1 < ntiles) {
-#pragma unroll
-          for (int e = 0; e < kStatPerThread; ++e) pre[e] = (ctid + 128 * e < 4 * TILE) ? fetch_stat(j + 1, ctid + 128 * e) : 0.f;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ctid < TILE) s.stats[j & 1][ctid] = pre;
+        if (j + 1 < ntiles) pre = fetch_stat(j + 1);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
+      // a warp whose wait ran out keeps walking the loop without touching TMEM so that the barrier above still matches
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
         atomicExch(a.status, 205u);
         ok = false;
-        break;
       }
+      if (!ok) continue;
       tc_fence_after();
-      const float *st_lse = s.stats[j & 1][0], *st_mu = s.stats[j & 1][1];
-      const float *st_delta = s.stats[j & 1][2], *st_dsum = s.stats[j & 1][3];
+      const float4 *st = s.stats[j & 1];
       const int nvalid = a.Ly - j * TILE;  // streamed rows in this tile (masking for the query owner)
 #pragma unroll
-      for (int c0 = 0; c0 < TILE; c0 += 32) {
-        uint32_t rs[32], ra[32];
-        float p[32], da[32];
-        tmem_ld32(tlane + kColS + c0, rs);
-        if (has_t && kDoK) tmem_ld32(tlane + kColA + c0, ra);
+      for (int c = 0; c < CH; c += 16) {
+        const int cs = col0 + c;  // first score column of this chunk
+        uint32_t rs[16], rd[16], ra[16], rc[16];
+        tmem_ld16(tlane + kColS + cs, rs);
+        if (has_t) tmem_ld16(tlane + kColSd + cs, rd);
+        if (has_t && kDoK) tmem_ld16(tlane + kColA + cs, ra);
+        if (kDoK) tmem_ld16(tlane + kColC + cs, rc);
         tc_wait_ld();
+        if (!kKV && nvalid < TILE) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float lse2 = kKV ? st_lse[c0 + i] : r_lse2;
-          float pv = fast_exp2(__uint_as_float(rs[i]) * sl2 - lse2);
-          if (!kKV) pv = (c0 + i < nvalid) ? pv : 0.f;
-          p[i] = pv;
-          da[i] = (has_t && kDoK) ? __uint_as_float(ra[i]) - (kKV ? st_delta[c0 + i] : r_delta) : 0.f;
+          for (int i = 0; i < 16; ++i)
+            if (cs + i >= nvalid) rs[i] = __float_as_uint(-INFINITY);  // key past the end: P = 0
         }
-        uint32_t rn[32];  // N = scale * sd - mu
-        if (has_t) {
-          tmem_ld32(tlane + kColSd + c0, rn);
-          tc_wait_ld();
+        uint32_t kp[8], kpn[8], kw1[8], kw2[8];
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            rn[i] = __float_as_uint(__uint_as_float(rn[i]) * a.scale - (kKV ? st_mu[c0 + i] : r_mu));
-        }
-        if (kDoV) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(p[2 * i], p[2 * i + 1]);
-          tmem_st16(tlane + kColS + c0 / 2, pk);
-          if (has_t) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[i] = pack2<T>(p[2 * i] * __uint_as_float(rn[2 * i]), p[2 * i + 1] * __uint_as_float(rn[2 * i + 1]));
-            tmem_st16(tlane + kColSd + c0 / 2, pk);
+        for (int i = 0; i < 8; ++i) {
+          const float4 s0 = kKV ? st[cs + 2 * i] : rstat, s1 = kKV ? st[cs + 2 * i + 1] : rstat;
+          const float2 sc2 = make_float2(__uint_as_float(rs[2 * i]), __uint_as_float(rs[2 * i + 1]));
+          const float2 t = __ffma2_rn(sc2, sl2x2, make_float2(-s0.x, -s1.x));
+          const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          const float2 sp = __fmul2_rn(p, scx2);
+          float2 n = make_float2(0.f, 0.f);
+          if (has_t)
+            n = __ffma2_rn(make_float2(__uint_as_float(rd[2 * i]), __uint_as_float(rd[2 * i + 1])), scx2,
+                           make_float2(-s0.y, -s1.y));
+          if (kDoV) {
+            kp[i] = pack2<T>(p.x, p.y);
+            if (has_t) {
+              const float2 pn = __fmul2_rn(p, n);
+              kpn[i] = pack2<T>(pn.x, pn.y);
+            }
           }
+          if (kDoK) {
+            float2 inner = __fadd2_rn(make_float2(__uint_as_float(rc[2 * i]), __uint_as_float(rc[2 * i + 1])),
+                                      make_float2(-s0.w, -s1.w));
+            if (has_t) {
+              const float2 da = __fadd2_rn(make_float2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1])),
+                                           make_float2(-s0.z, -s1.z));
+              const float2 w1 = __fmul2_rn(sp, da);
+              kw1[i] = pack2<T>(w1.x, w1.y);
+              inner = __ffma2_rn(da, n, inner);
+            }
+            const float2 w2 = __fmul2_rn(sp, inner);
+            kw2[i] = pack2<T>(w2.x, w2.y);
+          }
+        }
+        // 16 score columns become 8 packed operand columns, written at the start of this thread's own
+        // column range, over columns it has already consumed
+        const uint32_t oc = col0 + c / 2;
+        if (kDoV) {
+          tmem_st8(tlane + kColS + oc, kp);
+          if (has_t) tmem_st8(tlane + kColSd + oc, kpn);
         }
         if (kDoK) {
-          uint32_t rc[32], pk[16];
-          tmem_ld32(tlane + kColC + c0, rc);
-          tc_wait_ld();
-          if (has_t) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              pk[i] = pack2<T>(a.scale * p[2 * i] * da[2 * i], a.scale * p[2 * i + 1] * da[2 * i + 1]);
-            tmem_st16(tlane + kColA + c0 / 2, pk);
-          }
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float w[2];
-#pragma unroll
-            for (int t = 0; t < 2; ++t) {
-              const int e = 2 * i + t;
-              const float dsum = kKV ? st_dsum[c0 + e] : r_dsum;
-              const float nn = has_t ? __uint_as_float(rn[e]) : 0.f;
-              w[t] = a.scale * p[e] * (da[e] * nn + __uint_as_float(rc[e]) - dsum);
-            }
-            pk[i] = pack2<T>(w[0], w[1]);
-          }
-          tmem_st16(tlane + kColC + c0 / 2, pk);
+          if (has_t) tmem_st8(tlane + kColA + oc, kw1);
+          tmem_st8(tlane + kColC + oc, kw2);
         }
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.w_full);
     }
-    // ---- epilogue: accumulators -> 16-bit outputs
+    // ---- epilogue: accumulators -> 16-bit outputs, each thread half of the channels of its row
     if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, (ntiles - 1) & 1))) {
       atomicExch(a.status, 206u);
       ok = false;
@@ -381,12 +381,13 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     if (ok) {
       const int xr = x0 + row;
       const bool live = xr < a.Lx;
+      const int cbase = half * (D / 2);
       auto store_acc = [&](uint32_t col, const View &v) {
-        T *dst = static_cast<T *>(v.ptr) + v.offset(b, h, live ? xr : 0);
+        T *dst = static_cast<T *>(v.ptr) + v.offset(b, h, live ? xr : 0) + cbase;
 #pragma unroll
-        for (int c = 0; c < D; c += 32) {
+        for (int c = 0; c < D / 2; c += 32) {
           uint32_t r[32], pk[16];
-          tmem_ld32(tlane + col + c, r);
+          tmem_ld32(tlane + col + cbase + c, r);
           tc_wait_ld();
 #pragma unroll
           for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));

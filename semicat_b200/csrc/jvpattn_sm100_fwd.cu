@@ -48,7 +48,7 @@ struct FwdMaps {
 };
 
 template <int D, typename T>
-__global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_constant__ FwdMaps maps, FwdArgs a) {
+__global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(const __grid_constant__ FwdMaps maps, FwdArgs a) {
   extern __shared__ unsigned char smem_raw[];
   using Smem = FwdSmem<D>;
   Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -168,23 +168,30 @@ __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_consta
         break;
       }
       tc_fence_after();
-      uint32_t sv[64];
+      // the 64 scores of this row and the first half of Sd in flight at once, one wait
+      uint32_t sv[64], sd[32];
       {
         uint32_t(&lo)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[0]);
         uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
         tmem_ld32(tlane + kColS, lo);
         tmem_ld32(tlane + kColS + 32, hi);
+        tmem_ld32(tlane + kColSd, sd);
         tc_wait_ld();
       }
       const int nvalid = a.Lk - j * kBN;  // >= 1; < 64 only on the last tile
-      float mx = -INFINITY;
+      if (nvalid < 64) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float t = __uint_as_float(sv[c]) * sl2;
-        t = c < nvalid ? t : -INFINITY;
-        sv[c] = __float_as_uint(t);
-        mx = fmaxf(mx, t);
+        for (int c = 0; c < 64; ++c)
+          if (c >= nvalid) sv[c] = __float_as_uint(-INFINITY);
       }
+      // row max of the raw scores on four independent chains (scale > 0 commutes with the max)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) mx4[t] = fmaxf(mx4[t], __uint_as_float(sv[c + t]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
       // Keep the old reference max while the new one is at most 2^8 above it: O / Od' then need no rescale.
       float m_new = (mx - m > kRescaleThreshold) ? mx : m;
       if (j == 0) m_new = mx;
@@ -201,32 +208,35 @@ __global__ void __launch_bounds__(kThreads) sm100_fwd_kernel(const __grid_consta
           tmem_st32(tlane + kColO + c, r);
         }
       }
-      l *= alpha;
-      mu *= alpha;
       m = m_new;
-      float psum = 0.f, usum = 0.f;
+      // p = 2^(s * scale*log2e - m), u = p * scale * sd: packed two-wide fp32 arithmetic, two sum chains each
+      const float2 sl2x2 = make_float2(sl2, sl2), negm = make_float2(-m, -m), scx2 = make_float2(a.scale, a.scale);
+      float2 psum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      float2 usum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t sd[32], pk[16], uk[16];
-        tmem_ld32(tlane + kColSd + c0, sd);
-        tc_wait_ld();
+        uint32_t pk[16], uk[16];
+        if (c0 > 0) {
+          tmem_ld32(tlane + kColSd + c0, sd);
+          tc_wait_ld();
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(__uint_as_float(sv[c0 + 2 * i]) - m);
-          const float p1 = fast_exp2(__uint_as_float(sv[c0 + 2 * i + 1]) - m);
-          const float u0 = p0 * (__uint_as_float(sd[2 * i]) * a.scale);
-          const float u1 = p1 * (__uint_as_float(sd[2 * i + 1]) * a.scale);
-          psum += p0 + p1;
-          usum += u0 + u1;
-          pk[i] = pack2<T>(p0, p1);
-          uk[i] = pack2<T>(u0, u1);
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(sv[c0 + 2 * i]), __uint_as_float(sv[c0 + 2 * i + 1])), sl2x2, negm);
+          const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+          const float2 u = __fmul2_rn(__fmul2_rn(p, scx2),
+                                      make_float2(__uint_as_float(sd[2 * i]), __uint_as_float(sd[2 * i + 1])));
+          psum[i & 1] = __fadd2_rn(psum[i & 1], p);
+          usum[i & 1] = __fadd2_rn(usum[i & 1], u);
+          pk[i] = pack2<T>(p.x, p.y);
+          uk[i] = pack2<T>(u.x, u.y);
         }
         // 32 score columns become 16 packed operand columns, written over columns already consumed
         tmem_st16(tlane + kColS + c0 / 2, pk);
         tmem_st16(tlane + kColSd + c0 / 2, uk);
       }
-      l += psum;
-      mu += usum;
+      l = l * alpha + ((psum[0].x + psum[0].y) + (psum[1].x + psum[1].y));
+      mu = mu * alpha + ((usum[0].x + usum[0].y) + (usum[1].x + usum[1].y));
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.p_full);
