@@ -37,17 +37,17 @@ namespace {
 using namespace ptx;
 
 constexpr int kRows = 128;
-constexpr int kStages = 2;
 constexpr int kThreads = 320;        // TMA warp, MMA warp, 8 score-algebra warps
 constexpr int kComputeThreads = 256;
 
 template <int D, int TILE>
 struct BwdSmem {
   static constexpr int kBoxes = D / 64;
+  static constexpr int kStages = D == 64 ? 3 : 2;
   alignas(1024) uint16_t x[4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
-  uint64_t x_full, y_full[kStages], y_empty[kStages], s_full, w_full, done;
+  uint64_t x_full, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
   uint32_t tmem_base;
 };
 
@@ -122,15 +122,18 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   using Smem = BwdSmem<D, TILE>;
   Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kBoxes = D / 64;
+  constexpr int kStages = Smem::kStages;
   constexpr int kAcc = (kDoK ? 2 : 0) + (kDoV ? 2 : 0);
   constexpr uint32_t kColK = 0, kColKd = D;                         // dX0, dX1
   constexpr uint32_t kColV = kDoK ? 2 * D : 0, kColVd = kColV + D;  // dV, dVd
+  // two score regions that are in different phases of the pipeline: (S | Sd) and (A | C)
   constexpr uint32_t kColS = kAcc * D, kColSd = kColS + TILE, kColA = kColS + 2 * TILE, kColC = kColS + 3 * TILE;
   constexpr uint32_t kUsed = kAcc * D + 4 * TILE;
   static_assert(kUsed <= 512, "TMEM budget");
   constexpr uint32_t kTmemCols = kUsed <= 256 ? 256 : 512;
   constexpr bool kBf16 = IsBf16<T>::value;
   constexpr uint32_t kTileBytes = TILE * D * 2;
+  constexpr int CH = TILE / 2;  // score columns per compute thread and tile
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y, x0 = blockIdx.x * kRows;
@@ -143,8 +146,10 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       mbar_init(&s.y_full[i], 1);
       mbar_init(&s.y_empty[i], 1);
     }
-    mbar_init(&s.s_full, 1);
-    mbar_init(&s.w_full, kComputeThreads);
+    mbar_init(&s.s1_full, 1);
+    mbar_init(&s.s2_full, 1);
+    mbar_init(&s.c1_done, kComputeThreads);
+    mbar_init(&s.c2_done, kComputeThreads);
     mbar_init(&s.done, 1);
     fence_barrier_init();
   }
@@ -180,92 +185,121 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // Per streamed tile j the tensor core runs four groups, interleaved with the two halves of the score
+    // algebra so that it always has the next group queued while the compute warps work:
+    //   scores1(j): S, Sd            -> compute1(j): P, PoN (operands), keeps scale*P and N in registers
+    //   scores2(j): A, C             -> compute2(j): W1, W2 (operands)
+    //   outV(j):    dVd, dV += ...   needs compute1(j)         outK(j): dX1, dX0 += ...   needs compute2(j)
+    // issue order: scores1(0) scores2(0) | outV(j) scores1(j+1) outK(j) scores2(j+1) | ...
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kRows, TILE, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kRows, D, kBf16, false, true);
       // the X2 Y3^T term of C carries G Vd^T for the query owner but V gO^T for the key owner, and vice versa
       const bool term23 = kKV ? has_o : has_t;
       const bool term32 = kKV ? has_t : has_o;
-      bool ok = mbar_wait(&s.x_full, 0);
-      if (!ok) atomicExch(a.status, 202u);
-      bool init0 = false, init1 = false, initv = false, initvd = false;  // accumulators written at least once
-      for (int j = 0; ok && j < ntiles; ++j) {
+      auto xd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.x[t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
+      auto yd = [&](int st, int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
+      // one accumulator at a time, 16 channels per instruction
+      auto scores1 = [&](int j) -> bool {
         const int st = j % kStages;
-        if (!mbar_wait(&s.y_full[st], (j / kStages) & 1)) {
-          atomicExch(a.status, 203u);
-          break;
-        }
+        if (!mbar_wait(&s.y_full[st], (j / kStages) & 1)) return false;
         tc_fence_after();
-        // one accumulator at a time, 16 channels per instruction
-        auto xd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.x[t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
-        auto yd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColS, xd(0, kk), yd(0, kk), idesc_s, kk > 0);
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColS, xd(0, kk), yd(st, 0, kk), idesc_s, kk > 0);
         if (has_t) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            mma_ss(tmem + kColSd, xd(1, kk), yd(0, kk), idesc_s, kk > 0);
-            mma_ss(tmem + kColSd, xd(0, kk), yd(1, kk), idesc_s, true);
-          }
-          if (kDoK) {
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColA, xd(2, kk), yd(2, kk), idesc_s, kk > 0);
+            mma_ss(tmem + kColSd, xd(1, kk), yd(st, 0, kk), idesc_s, kk > 0);
+            mma_ss(tmem + kColSd, xd(0, kk), yd(st, 1, kk), idesc_s, true);
           }
         }
-        if (kDoK) {
-          bool c_started = false;
-          if (term23) {
+        tc_commit(&s.s1_full);
+        return true;
+      };
+      auto scores2 = [&](int j) {
+        if (!kDoK) return;
+        const int st = j % kStages;  // already resident: scores1(j) waited for it
+        if (has_t) {
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(2, kk), yd(3, kk), idesc_s, c_started || kk > 0);
-            c_started = true;
-          }
-          if (term32) {
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(3, kk), yd(2, kk), idesc_s, c_started || kk > 0);
-          }
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColA, xd(2, kk), yd(st, 2, kk), idesc_s, kk > 0);
         }
-        tc_commit(&s.s_full);
-        if (!mbar_wait(&s.w_full, j & 1)) {
+        bool c_started = false;
+        if (term23) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(2, kk), yd(st, 3, kk), idesc_s, c_started || kk > 0);
+          c_started = true;
+        }
+        if (term32) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(3, kk), yd(st, 2, kk), idesc_s, c_started || kk > 0);
+        }
+        tc_commit(&s.s2_full);
+      };
+      constexpr uint32_t lbo = TILE * 128;  // bytes between 64-channel column blocks of a Y tile
+      auto yb = [&](int st, int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][0]) + kk * 2048, lbo, 1024); };
+      // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the start
+      // of its own column range (see the score-algebra warps)
+      auto oa = [&](int kk) -> uint32_t { return ((16 * kk) / CH) * CH + ((16 * kk) % CH) / 2; };
+      bool init0 = false, init1 = false, initv = false, initvd = false;  // accumulators written at least once
+      bool ok = mbar_wait(&s.x_full, 0);
+      if (!ok) atomicExch(a.status, 202u);
+      if (ok) {
+        if (!scores1(0)) {
+          atomicExch(a.status, 203u);
+          ok = false;
+        } else {
+          scores2(0);
+        }
+      }
+      for (int j = 0; ok && j < ntiles; ++j) {
+        const int st = j % kStages;
+        if (!mbar_wait(&s.c1_done, j & 1)) {
           atomicExch(a.status, 204u);
           break;
         }
         tc_fence_after();
-        constexpr uint32_t lbo = TILE * 128;  // bytes between 64-channel column blocks of a Y tile
+        if (kDoV) {
 #pragma unroll
-        for (int kk = 0; kk < TILE / 16; ++kk) {
-          auto yb = [&](int t) { return make_smem_desc(smem_u32(s.y[st][t][0]) + kk * 2048, lbo, 1024); };
-          // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the
-          // start of its own column range (see the score-algebra warps)
-          constexpr int CH = TILE / 2;
-          const uint32_t oa = ((16 * kk) / CH) * CH + ((16 * kk) % CH) / 2;
-          if (kDoK) {
+          for (int kk = 0; kk < TILE / 16; ++kk) {
             if (has_t) {
-              mma_ts(tmem + kColKd, tmem + kColA + oa, yb(0), idesc_o, init1);   // dX1 += W1 Y0
-              mma_ts(tmem + kColK, tmem + kColA + oa, yb(1), idesc_o, init0);    // dX0 += W1 Y1
-              init0 = init1 = true;
-            }
-            mma_ts(tmem + kColK, tmem + kColC + oa, yb(0), idesc_o, init0);      // dX0 += W2 Y0
-            init0 = true;
-          }
-          if (kDoV) {
-            if (has_t) {
-              mma_ts(tmem + kColVd, tmem + kColS + oa, yb(2), idesc_o, initvd);  // dVd += P G
-              mma_ts(tmem + kColV, tmem + kColSd + oa, yb(2), idesc_o, initv);   // dV  += (P o N) G
+              mma_ts(tmem + kColVd, tmem + kColS + oa(kk), yb(st, 2, kk), idesc_o, initvd);  // dVd += P G
+              mma_ts(tmem + kColV, tmem + kColSd + oa(kk), yb(st, 2, kk), idesc_o, initv);   // dV  += (P o N) G
               initv = initvd = true;
             }
             if (has_o) {
-              mma_ts(tmem + kColV, tmem + kColS + oa, yb(3), idesc_o, initv);    // dV  += P gO
+              mma_ts(tmem + kColV, tmem + kColS + oa(kk), yb(st, 3, kk), idesc_o, initv);    // dV  += P gO
               initv = true;
             }
           }
         }
+        if (j + 1 < ntiles && !scores1(j + 1)) {
+          atomicExch(a.status, 203u);
+          break;
+        }
+        if (kDoK) {
+          if (!mbar_wait(&s.c2_done, j & 1)) {
+            atomicExch(a.status, 207u);
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < TILE / 16; ++kk) {
+            if (has_t) {
+              mma_ts(tmem + kColKd, tmem + kColA + oa(kk), yb(st, 0, kk), idesc_o, init1);   // dX1 += W1 Y0
+              mma_ts(tmem + kColK, tmem + kColA + oa(kk), yb(st, 1, kk), idesc_o, init0);    // dX0 += W1 Y1
+              init0 = init1 = true;
+            }
+            mma_ts(tmem + kColK, tmem + kColC + oa(kk), yb(st, 0, kk), idesc_o, init0);      // dX0 += W2 Y0
+            init0 = true;
+          }
+        }
         tc_commit(&s.y_empty[st]);
         tc_commit(&s.done);
+        if (j + 1 < ntiles) scores2(j + 1);
       }
     }
   } else {
     // ------------------------------------------------------------------ score algebra: two threads per owned row
-    constexpr int CH = TILE / 2;  // score columns per thread and tile
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
@@ -301,7 +335,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       // a warp whose wait ran out keeps walking the loop without touching TMEM so that the barrier above still matches
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s1_full, j & 1))) {
         atomicExch(a.status, 205u);
         ok = false;
       }
@@ -309,32 +343,33 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       tc_fence_after();
       const float4 *st = s.stats[j & 1];
       const int nvalid = a.Ly - j * TILE;  // streamed rows in this tile (masking for the query owner)
+      // ---- first half: P = exp2(s*scale*log2e - lse*log2e), N = scale*sd - mu
+      float2 sp[CH / 2], nn[CH / 2];  // scale * P and N, carried into the second half
 #pragma unroll
       for (int c = 0; c < CH; c += 16) {
         const int cs = col0 + c;  // first score column of this chunk
-        uint32_t rs[16], rd[16], ra[16], rc[16];
+        uint32_t rs[16], rd[16];
         tmem_ld16(tlane + kColS + cs, rs);
         if (has_t) tmem_ld16(tlane + kColSd + cs, rd);
-        if (has_t && kDoK) tmem_ld16(tlane + kColA + cs, ra);
-        if (kDoK) tmem_ld16(tlane + kColC + cs, rc);
         tc_wait_ld();
         if (!kKV && nvalid < TILE) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
             if (cs + i >= nvalid) rs[i] = __float_as_uint(-INFINITY);  // key past the end: P = 0
         }
-        uint32_t kp[8], kpn[8], kw1[8], kw2[8];
+        uint32_t kp[8], kpn[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 s0 = kKV ? st[cs + 2 * i] : rstat, s1 = kKV ? st[cs + 2 * i + 1] : rstat;
-          const float2 sc2 = make_float2(__uint_as_float(rs[2 * i]), __uint_as_float(rs[2 * i + 1]));
-          const float2 t = __ffma2_rn(sc2, sl2x2, make_float2(-s0.x, -s1.x));
+          const float2 t = __ffma2_rn(make_float2(__uint_as_float(rs[2 * i]), __uint_as_float(rs[2 * i + 1])), sl2x2,
+                                      make_float2(-s0.x, -s1.x));
           const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-          const float2 sp = __fmul2_rn(p, scx2);
           float2 n = make_float2(0.f, 0.f);
           if (has_t)
             n = __ffma2_rn(make_float2(__uint_as_float(rd[2 * i]), __uint_as_float(rd[2 * i + 1])), scx2,
                            make_float2(-s0.y, -s1.y));
+          sp[c / 2 + i] = __fmul2_rn(p, scx2);
+          nn[c / 2 + i] = n;
           if (kDoV) {
             kp[i] = pack2<T>(p.x, p.y);
             if (has_t) {
@@ -342,35 +377,54 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
               kpn[i] = pack2<T>(pn.x, pn.y);
             }
           }
-          if (kDoK) {
-            float2 inner = __fadd2_rn(make_float2(__uint_as_float(rc[2 * i]), __uint_as_float(rc[2 * i + 1])),
-                                      make_float2(-s0.w, -s1.w));
-            if (has_t) {
-              const float2 da = __fadd2_rn(make_float2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1])),
-                                           make_float2(-s0.z, -s1.z));
-              const float2 w1 = __fmul2_rn(sp, da);
-              kw1[i] = pack2<T>(w1.x, w1.y);
-              inner = __ffma2_rn(da, n, inner);
-            }
-            const float2 w2 = __fmul2_rn(sp, inner);
-            kw2[i] = pack2<T>(w2.x, w2.y);
-          }
         }
-        // 16 score columns become 8 packed operand columns, written at the start of this thread's own
-        // column range, over columns it has already consumed
-        const uint32_t oc = col0 + c / 2;
         if (kDoV) {
-          tmem_st8(tlane + kColS + oc, kp);
-          if (has_t) tmem_st8(tlane + kColSd + oc, kpn);
+          // 16 score columns become 8 packed operand columns, written at the start of this thread's own
+          // column range, over columns it has already consumed
+          tmem_st8(tlane + kColS + col0 + c / 2, kp);
+          if (has_t) tmem_st8(tlane + kColSd + col0 + c / 2, kpn);
         }
-        if (kDoK) {
-          if (has_t) tmem_st8(tlane + kColA + oc, kw1);
-          tmem_st8(tlane + kColC + oc, kw2);
+      }
+      if (kDoV) tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
+      if (!kDoK) continue;
+      // ---- second half: W1 = scale P (A - delta), W2 = scale P ((A - delta) N + C - dsum)
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.s2_full, j & 1))) {
+        atomicExch(a.status, 208u);
+        ok = false;
+        continue;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < CH; c += 16) {
+        const int cs = col0 + c;
+        uint32_t ra[16], rc[16];
+        if (has_t) tmem_ld16(tlane + kColA + cs, ra);
+        tmem_ld16(tlane + kColC + cs, rc);
+        tc_wait_ld();
+        uint32_t kw1[8], kw2[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 s0 = kKV ? st[cs + 2 * i] : rstat, s1 = kKV ? st[cs + 2 * i + 1] : rstat;
+          float2 inner = __fadd2_rn(make_float2(__uint_as_float(rc[2 * i]), __uint_as_float(rc[2 * i + 1])),
+                                    make_float2(-s0.w, -s1.w));
+          if (has_t) {
+            const float2 da = __fadd2_rn(make_float2(__uint_as_float(ra[2 * i]), __uint_as_float(ra[2 * i + 1])),
+                                         make_float2(-s0.z, -s1.z));
+            const float2 w1 = __fmul2_rn(sp[c / 2 + i], da);
+            kw1[i] = pack2<T>(w1.x, w1.y);
+            inner = __ffma2_rn(da, nn[c / 2 + i], inner);
+          }
+          const float2 w2 = __fmul2_rn(sp[c / 2 + i], inner);
+          kw2[i] = pack2<T>(w2.x, w2.y);
         }
+        if (has_t) tmem_st8(tlane + kColA + col0 + c / 2, kw1);
+        tmem_st8(tlane + kColC + col0 + c / 2, kw2);
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&s.w_full);
+      mbar_arrive(&s.c2_done);
     }
     // ---- epilogue: accumulators -> 16-bit outputs, each thread half of the channels of its row
     if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, (ntiles - 1) & 1))) {
