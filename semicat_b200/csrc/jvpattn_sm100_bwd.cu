@@ -27,6 +27,8 @@
 //   warp 1      MMA issuer
 //   warps 2..9  two threads per owned row (each on half of the tile's columns): score algebra, operand
 //               write-back over consumed score columns, epilogue
+#include <algorithm>
+
 #include "jvpattn_common.cuh"
 #include "sm100_attn.cuh"
 #include "sm100_ptx.cuh"
@@ -43,13 +45,45 @@ constexpr int kComputeThreads = 256;
 template <int D, int TILE>
 struct BwdSmem {
   static constexpr int kBoxes = D / 64;
-  static constexpr int kStages = D == 64 ? 3 : 2;
-  alignas(1024) uint16_t x[4][kBoxes][kRows * 64];
+  static constexpr int kXBuf = D == 64 ? 2 : 1;  // owned-row tiles are double buffered where shared memory allows
+  static constexpr int kStages = 2;
+  alignas(1024) uint16_t x[kXBuf][4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
-  uint64_t x_full, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
+  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
   uint32_t tmem_base;
 };
+
+// Optional event trace of CTA 0 (debug builds only: -DJVPATTN_TRACE): (tag, clock64) pairs.
+#ifdef JVPATTN_TRACE
+__device__ unsigned long long g_trace[2][2][4096];  // [query | key owner][MMA thread | compute thread 0][event]
+#define JVP_TRACE_DECL(role) unsigned trace_n_ = 0; const int trace_role_ = (role)
+#define JVP_TRACE(tag)                                                                                        \
+  do {                                                                                                        \
+    if (blockIdx.x == 0 && trace_n_ < 4096)                                                                   \
+      g_trace[kKV ? 1 : 0][trace_role_][trace_n_++] = ((unsigned long long)(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
+  } while (0)
+#else
+#define JVP_TRACE_DECL(role) \
+  do {                       \
+  } while (0)
+#define JVP_TRACE(tag) \
+  do {                 \
+  } while (0)
+#endif
+
+// Number of SMs of the current device (cached per device id).
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
 
 struct BwdMaps {
   CUtensorMap x[4], y[4];
@@ -60,7 +94,7 @@ struct BwdKernelArgs {
   const float *lse, *mu;  // [B, H, stat_len]
   const float *delta, *dsum;
   unsigned int *status;
-  int H, Lx, Ly, Lq, stat_len;  // Lx rows on the owner side, Ly on the streamed side
+  int B, H, Lx, Ly, Lq, stat_len;  // Lx rows on the owner side, Ly on the streamed side
   int xmask, ymask;             // which of the four X / Y tensors are loaded
   int has_t, has_o;
   float scale;
@@ -135,13 +169,27 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   constexpr uint32_t kTileBytes = TILE * D * 2;
   constexpr int CH = TILE / 2;  // score columns per compute thread and tile
 
+  constexpr int kXBuf = Smem::kXBuf;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y, x0 = blockIdx.x * kRows;
   const int ntiles = (a.Ly + TILE - 1) / TILE;
   const bool has_t = a.has_t != 0, has_o = a.has_o != 0;
+  // Persistent CTA: work item = 128 owned rows of one (batch, head); items blockIdx.x, + gridDim.x, ...
+  // Counters shared by all roles: n = items done by this CTA, g = streamed tiles done (across items).
+  const int nx = (a.Lx + kRows - 1) / kRows;
+  const int items = a.B * a.H * nx;
+  auto decode = [&](int it, int &bb, int &hh, int &xx0) {
+    xx0 = (it % nx) * kRows;
+    const int bh = it / nx;
+    hh = bh % a.H;
+    bb = bh / a.H;
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(&s.x_full, 1);
+    for (int i = 0; i < kXBuf; ++i) {
+      mbar_init(&s.x_full[i], 1);
+      mbar_init(&s.x_empty[i], 1);
+    }
+    mbar_init(&s.acc_free, kComputeThreads);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&s.y_full[i], 1);
       mbar_init(&s.y_empty[i], 1);
@@ -167,20 +215,32 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     if (lane == 0) {
       prefetch_tensormap(&maps.x[0]);
       prefetch_tensormap(&maps.y[0]);
-      mbar_expect_tx(&s.x_full, __popc(a.xmask) * kRows * D * 2);
-      for (int t = 0; t < 4; ++t)
-        if (a.xmask >> t & 1)
-          for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[t][x], &maps.x[t], &s.x_full, 64 * x, x0, h, b);
-      for (int j = 0; j < ntiles; ++j) {
-        const int st = j % kStages;
-        if (!mbar_wait(&s.y_empty[st], ((j / kStages) & 1) ^ 1)) {
-          atomicExch(a.status, 201u);
+      int n = 0, g = 0;
+      bool ok = true;
+      for (int it = blockIdx.x; ok && it < items; it += gridDim.x, ++n) {
+        int b, h, x0;
+        decode(it, b, h, x0);
+        const int xb = n % kXBuf;
+        if (!mbar_wait(&s.x_empty[xb], ((n / kXBuf) & 1) ^ 1)) {
+          atomicExch(a.status, 209u);
           break;
         }
-        mbar_expect_tx(&s.y_full[st], __popc(a.ymask) * kTileBytes);
+        mbar_expect_tx(&s.x_full[xb], __popc(a.xmask) * kRows * D * 2);
         for (int t = 0; t < 4; ++t)
-          if (a.ymask >> t & 1)
-            for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][t][x], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
+          if (a.xmask >> t & 1)
+            for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[xb][t][x], &maps.x[t], &s.x_full[xb], 64 * x, x0, h, b);
+        for (int j = 0; j < ntiles; ++j, ++g) {
+          const int st = g % kStages;
+          if (!mbar_wait(&s.y_empty[st], ((g / kStages) & 1) ^ 1)) {
+            atomicExch(a.status, 201u);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&s.y_full[st], __popc(a.ymask) * kTileBytes);
+          for (int t = 0; t < 4; ++t)
+            if (a.ymask >> t & 1)
+              for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][t][x], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
+        }
       }
     }
   } else if (warp == 1) {
@@ -192,110 +252,162 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     //   outV(j):    dVd, dV += ...   needs compute1(j)         outK(j): dX1, dX0 += ...   needs compute2(j)
     // issue order: scores1(0) scores2(0) | outV(j) scores1(j+1) outK(j) scores2(j+1) | ...
     if (lane == 0) {
+      JVP_TRACE_DECL(0);
       constexpr uint32_t idesc_s = make_idesc(kRows, TILE, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kRows, D, kBf16, false, true);
       // the X2 Y3^T term of C carries G Vd^T for the query owner but V gO^T for the key owner, and vice versa
       const bool term23 = kKV ? has_o : has_t;
       const bool term32 = kKV ? has_t : has_o;
-      auto xd = [&](int t, int kk) { return make_smem_desc(smem_u32(s.x[t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
-      auto yd = [&](int st, int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][kk >> 2]) + (kk & 3) * 32, 16, 1024); };
-      // one accumulator at a time, 16 channels per instruction
-      auto scores1 = [&](int j) -> bool {
-        const int st = j % kStages;
-        if (!mbar_wait(&s.y_full[st], (j / kStages) & 1)) return false;
+      // Low descriptor words: one runtime base (shared memory offset >> 4) plus compile-time tile offsets, so
+      // that issuing an MMA costs a handful of instructions (the issue rate of this one thread bounds the kernel).
+      const uint32_t base16 = smem_u32(&s) >> 4;
+      constexpr uint32_t kXTile = kRows * 128, kYTile = TILE * 128;  // bytes of one 64-channel box
+      auto xbase = [&](int xb) { return base16 + (uint32_t)((offsetof(Smem, x) + (size_t)xb * 4 * kBoxes * kXTile) >> 4); };
+      auto ybase = [&](int st) { return base16 + (uint32_t)((offsetof(Smem, y) + (size_t)st * 4 * kBoxes * kYTile) >> 4); };
+      auto xd = [&](uint32_t xlo, int t, int kk) {
+        return xlo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kXTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+      };
+      auto yd = [&](uint32_t ylo, int t, int kk) {
+        return ylo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kYTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+      };
+      // one accumulator at a time, 16 channels per instruction.  g = tile counter (stage / parity), xb = X buffer,
+      // last = this is the item's last tile (its X tiles are released once no later score MMA needs them)
+      auto scores1 = [&](int g, int xb, bool last) -> bool {
+        const int st = g % kStages;
+        if (!mbar_wait(&s.y_full[st], (g / kStages) & 1)) return false;
         tc_fence_after();
+        const uint32_t xlo = xbase(xb), ylo = ybase(st);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColS, xd(0, kk), yd(st, 0, kk), idesc_s, kk > 0);
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, xd(xlo, 0, kk), yd(ylo, 0, kk), idesc_s, kk > 0);
         if (has_t) {
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            mma_ss(tmem + kColSd, xd(1, kk), yd(st, 0, kk), idesc_s, kk > 0);
-            mma_ss(tmem + kColSd, xd(0, kk), yd(st, 1, kk), idesc_s, true);
+            mma_ss_lo(tmem + kColSd, xd(xlo, 1, kk), yd(ylo, 0, kk), idesc_s, kk > 0);
+            mma_ss_lo(tmem + kColSd, xd(xlo, 0, kk), yd(ylo, 1, kk), idesc_s, true);
           }
         }
         tc_commit(&s.s1_full);
+        if (!kDoK && last) tc_commit(&s.x_empty[xb]);
+        JVP_TRACE(1);
         return true;
       };
-      auto scores2 = [&](int j) {
+      auto scores2 = [&](int g, int xb, bool last) {
         if (!kDoK) return;
-        const int st = j % kStages;  // already resident: scores1(j) waited for it
+        const int st = g % kStages;  // already resident: scores1 waited for it
+        const uint32_t xlo = xbase(xb), ylo = ybase(st);
         if (has_t) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColA, xd(2, kk), yd(st, 2, kk), idesc_s, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColA, xd(xlo, 2, kk), yd(ylo, 2, kk), idesc_s, kk > 0);
         }
         bool c_started = false;
         if (term23) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(2, kk), yd(st, 3, kk), idesc_s, c_started || kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_ss_lo(tmem + kColC, xd(xlo, 2, kk), yd(ylo, 3, kk), idesc_s, c_started || kk > 0);
           c_started = true;
         }
         if (term32) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + kColC, xd(3, kk), yd(st, 2, kk), idesc_s, c_started || kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_ss_lo(tmem + kColC, xd(xlo, 3, kk), yd(ylo, 2, kk), idesc_s, c_started || kk > 0);
         }
         tc_commit(&s.s2_full);
+        if (last) tc_commit(&s.x_empty[xb]);
+        JVP_TRACE(6);
       };
       constexpr uint32_t lbo = TILE * 128;  // bytes between 64-channel column blocks of a Y tile
-      auto yb = [&](int st, int t, int kk) { return make_smem_desc(smem_u32(s.y[st][t][0]) + kk * 2048, lbo, 1024); };
+      auto yb = [&](uint32_t ylo, int t, int kk) {
+        return ylo + (uint32_t)((t * kBoxes * kYTile + kk * 2048) >> 4) + desc_lo_mn_major(lbo);
+      };
       // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the start
       // of its own column range (see the score-algebra warps)
       auto oa = [&](int kk) -> uint32_t { return ((16 * kk) / CH) * CH + ((16 * kk) % CH) / 2; };
-      bool init0 = false, init1 = false, initv = false, initvd = false;  // accumulators written at least once
-      bool ok = mbar_wait(&s.x_full, 0);
-      if (!ok) atomicExch(a.status, 202u);
+      // the stream of (item, tile) pairs this CTA walks; `n` counts items, `g` tiles
+      int it = blockIdx.x, j = 0, n = 0, g = 0;
+      bool ok = it < items;
+      if (ok && !mbar_wait(&s.x_full[0], 0)) {
+        atomicExch(a.status, 202u);
+        ok = false;
+      }
       if (ok) {
-        if (!scores1(0)) {
+        if (!scores1(0, 0, ntiles == 1)) {
           atomicExch(a.status, 203u);
           ok = false;
         } else {
-          scores2(0);
+          scores2(0, 0, ntiles == 1);
         }
       }
-      for (int j = 0; ok && j < ntiles; ++j) {
-        const int st = j % kStages;
-        if (!mbar_wait(&s.c1_done, j & 1)) {
+      bool init0 = false, init1 = false, initv = false, initvd = false;  // accumulators written in this item
+      while (ok) {
+        const int st = g % kStages;
+        // successor in the stream
+        int it2 = it, j2 = j + 1, n2 = n;
+        if (j2 == ntiles) {
+          it2 = it + gridDim.x;
+          j2 = 0;
+          n2 = n + 1;
+        }
+        const bool has_next = it2 < items;
+        if (j == 0) init0 = init1 = initv = initvd = false;
+        if (!mbar_wait(&s.c1_done, g & 1)) {
           atomicExch(a.status, 204u);
           break;
         }
+        JVP_TRACE(2);
+        if (j == 0 && !mbar_wait(&s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
+          atomicExch(a.status, 210u);
+          break;
+        }
         tc_fence_after();
+        const uint32_t ylo_out = ybase(st);
         if (kDoV) {
 #pragma unroll
           for (int kk = 0; kk < TILE / 16; ++kk) {
             if (has_t) {
-              mma_ts(tmem + kColVd, tmem + kColS + oa(kk), yb(st, 2, kk), idesc_o, initvd);  // dVd += P G
-              mma_ts(tmem + kColV, tmem + kColSd + oa(kk), yb(st, 2, kk), idesc_o, initv);   // dV  += (P o N) G
+              mma_ts_lo(tmem + kColVd, tmem + kColS + oa(kk), yb(ylo_out, 2, kk), idesc_o, initvd);  // dVd += P G
+              mma_ts_lo(tmem + kColV, tmem + kColSd + oa(kk), yb(ylo_out, 2, kk), idesc_o, initv);   // dV  += (P o N) G
               initv = initvd = true;
             }
             if (has_o) {
-              mma_ts(tmem + kColV, tmem + kColS + oa(kk), yb(st, 3, kk), idesc_o, initv);    // dV  += P gO
+              mma_ts_lo(tmem + kColV, tmem + kColS + oa(kk), yb(ylo_out, 3, kk), idesc_o, initv);    // dV  += P gO
               initv = true;
             }
           }
         }
-        if (j + 1 < ntiles && !scores1(j + 1)) {
-          atomicExch(a.status, 203u);
-          break;
+        if (has_next) {
+          if (j2 == 0 && !mbar_wait(&s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
+            atomicExch(a.status, 202u);
+            break;
+          }
+          if (!scores1(g + 1, n2 % kXBuf, j2 == ntiles - 1)) {
+            atomicExch(a.status, 203u);
+            break;
+          }
         }
         if (kDoK) {
-          if (!mbar_wait(&s.c2_done, j & 1)) {
+          if (!mbar_wait(&s.c2_done, g & 1)) {
             atomicExch(a.status, 207u);
             break;
           }
+          JVP_TRACE(4);
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < TILE / 16; ++kk) {
             if (has_t) {
-              mma_ts(tmem + kColKd, tmem + kColA + oa(kk), yb(st, 0, kk), idesc_o, init1);   // dX1 += W1 Y0
-              mma_ts(tmem + kColK, tmem + kColA + oa(kk), yb(st, 1, kk), idesc_o, init0);    // dX0 += W1 Y1
+              mma_ts_lo(tmem + kColKd, tmem + kColA + oa(kk), yb(ylo_out, 0, kk), idesc_o, init1);   // dX1 += W1 Y0
+              mma_ts_lo(tmem + kColK, tmem + kColA + oa(kk), yb(ylo_out, 1, kk), idesc_o, init0);    // dX0 += W1 Y1
               init0 = init1 = true;
             }
-            mma_ts(tmem + kColK, tmem + kColC + oa(kk), yb(st, 0, kk), idesc_o, init0);      // dX0 += W2 Y0
+            mma_ts_lo(tmem + kColK, tmem + kColC + oa(kk), yb(ylo_out, 0, kk), idesc_o, init0);      // dX0 += W2 Y0
             init0 = true;
           }
         }
         tc_commit(&s.y_empty[st]);
-        tc_commit(&s.done);
-        if (j + 1 < ntiles) scores2(j + 1);
+        if (j == ntiles - 1) tc_commit(&s.done);
+        JVP_TRACE(5);
+        if (!has_next) break;
+        scores2(g + 1, n2 % kXBuf, j2 == ntiles - 1);
+        it = it2; j = j2; n = n2; ++g;
       }
     }
   } else {
@@ -305,9 +417,30 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     const int row = quad * 32 + lane;
     const int col0 = half * CH;
     const int ctid = threadIdx.x - 64;  // 0..255 among the compute threads
+#ifdef JVPATTN_TRACE
+    unsigned trace_n_ = ctid == 0 ? 0u : 4096u;  // only compute thread 0 records
+    const int trace_role_ = 1;
+#endif
     const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
     const float sl2 = a.scale * kLog2e;
     const float2 sl2x2 = make_float2(sl2, sl2), scx2 = make_float2(a.scale, a.scale);
+    // per-column statistics of the key owner: the first TILE compute threads fetch one query column each,
+    // one tile ahead (also across items), and publish it through shared memory
+    auto fetch_stat = [&](int it_, int j_) -> float4 {
+      int bb, hh, xx;
+      decode(it_, bb, hh, xx);
+      const int col = j_ * TILE + ctid;
+      if (ctid >= TILE || col >= a.Lq) return make_float4(INFINITY, 0.f, 0.f, 0.f);  // padded query: P = 0
+      const size_t si = ((size_t)bb * a.H + hh) * a.stat_len + col;
+      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
+    };
+    float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (kKV && blockIdx.x < items) pre = fetch_stat(blockIdx.x, 0);
+    bool ok = true;
+    int n = 0, g = 0;
+   for (int it = blockIdx.x; it < items; it += gridDim.x, ++n) {
+    int b, h, x0;
+    decode(it, b, h, x0);
     const size_t stat_base = ((size_t)b * a.H + h) * a.stat_len;
     // per-row statistics of the query owner: {lse * log2e, mu, delta, dsum}
     float4 rstat = make_float4(INFINITY, 0.f, 0.f, 0.f);
@@ -317,31 +450,22 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       rstat.z = a.delta[stat_base + x0 + row];
       rstat.w = a.dsum[stat_base + x0 + row];
     }
-    // per-column statistics of the key owner: the first TILE compute threads fetch one query column each,
-    // one tile ahead, and publish it through shared memory
-    auto fetch_stat = [&](int j) -> float4 {
-      const int col = j * TILE + ctid;
-      if (ctid >= TILE || col >= a.Lq) return make_float4(INFINITY, 0.f, 0.f, 0.f);  // padded query: P = 0
-      const size_t si = stat_base + col;
-      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
-    };
-    float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (kKV) pre = fetch_stat(0);
-    bool ok = true;
-    for (int j = 0; j < ntiles; ++j) {
+    for (int j = 0; j < ntiles; ++j, ++g) {
       if (kKV) {
-        if (ctid < TILE) s.stats[j & 1][ctid] = pre;
-        if (j + 1 < ntiles) pre = fetch_stat(j + 1);
+        if (ctid < TILE) s.stats[g & 1][ctid] = pre;
+        if (j + 1 < ntiles) pre = fetch_stat(it, j + 1);
+        else if (it + (int)gridDim.x < items) pre = fetch_stat(it + gridDim.x, 0);
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      // a warp whose wait ran out keeps walking the loop without touching TMEM so that the barrier above still matches
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s1_full, j & 1))) {
+      // a warp whose wait ran out keeps walking the loops without touching TMEM so that the barrier above still matches
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s1_full, g & 1))) {
         atomicExch(a.status, 205u);
         ok = false;
       }
       if (!ok) continue;
+      JVP_TRACE(10);
       tc_fence_after();
-      const float4 *st = s.stats[j & 1];
+      const float4 *st = s.stats[g & 1];
       const int nvalid = a.Ly - j * TILE;  // streamed rows in this tile (masking for the query owner)
       // ---- first half: P = exp2(s*scale*log2e - lse*log2e), N = scale*sd - mu
       float2 sp[CH / 2], nn[CH / 2];  // scale * P and N, carried into the second half
@@ -388,13 +512,15 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       if (kDoV) tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
+      JVP_TRACE(11);
       if (!kDoK) continue;
       // ---- second half: W1 = scale P (A - delta), W2 = scale P ((A - delta) N + C - dsum)
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.s2_full, j & 1))) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&s.s2_full, g & 1))) {
         atomicExch(a.status, 208u);
         ok = false;
         continue;
       }
+      JVP_TRACE(12);
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < CH; c += 16) {
@@ -425,12 +551,14 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.c2_done);
+      JVP_TRACE(13);
     }
-    // ---- epilogue: accumulators -> 16-bit outputs, each thread half of the channels of its row
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, (ntiles - 1) & 1))) {
+    // ---- epilogue of the item: accumulators -> 16-bit outputs, each thread half of the channels of its row
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, n & 1))) {
       atomicExch(a.status, 206u);
       ok = false;
     }
+    JVP_TRACE(14);
     tc_fence_after();
     if (ok) {
       const int xr = x0 + row;
@@ -460,7 +588,11 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         store_acc(kColV, a.out[2]);
         if (has_t) store_acc(kColVd, a.out[3]);
       }
+      tc_fence_before();
+      mbar_arrive(&s.acc_free);  // the next item may overwrite the accumulators
+      JVP_TRACE(15);
     }
+   }  // items
   }
 
   tc_fence_before();
@@ -497,13 +629,14 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
     ka.out[0] = a.dq; ka.out[1] = a.dtq;
   }
   ka.lse = a.lse; ka.mu = a.mu; ka.delta = delta; ka.dsum = dsum; ka.status = a.status;
-  ka.H = a.H; ka.Lx = Lx; ka.Ly = Ly; ka.Lq = a.Lq; ka.stat_len = a.stat_len;
+  ka.B = a.B; ka.H = a.H; ka.Lx = Lx; ka.Ly = Ly; ka.Lq = a.Lq; ka.stat_len = a.stat_len;
   ka.has_t = has_t; ka.has_o = has_o; ka.scale = a.scale;
   auto kernel = sm100_bwd_kernel<D, TILE, kKV, kDoK, kDoV, T>;
   const size_t smem = sizeof(BwdSmem<D, TILE>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  dim3 grid((Lx + kRows - 1) / kRows, a.H, a.B);
+  const int64_t items = (int64_t)a.B * a.H * ((Lx + kRows - 1) / kRows);
+  dim3 grid((unsigned)std::min<int64_t>(items, sm_count()));  // persistent: one CTA per SM walks the items
   {
     LaunchScope scope(kKV ? kIdBwdKeyTc : kIdBwdQueryTc, stream);
     kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
@@ -548,6 +681,17 @@ size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_l
   size_t bytes = (size_t)2 * B * H * stat_len * sizeof(float);
   return (bytes + 255) / 256 * 256;
 }
+
+#ifdef JVPATTN_TRACE
+extern "C" int jvpattn_trace_read(unsigned long long *host) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
+  cudaMemset(nullptr, 0, 0);
+  static unsigned long long zeros[2][2][4096];
+  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
+  return 0;
+}
+#endif
 
 bool sm100_bwd_supported(const BwdArgs &a) {
   if (a.D != 64 && a.D != 128) return false;

@@ -111,6 +111,8 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kBM, kBN, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBM, D, kBf16, false, true);
+      const uint32_t base16 = smem_u32(&s) >> 4;
+      constexpr uint32_t kQTile = kBM * 128, kKvTile = kBN * 128;  // bytes of one 64-channel box
       bool ok = mbar_wait(&s.q_full, 0);
       if (!ok) atomicExch(a.status, 102u);
       for (int j = 0; ok && j < ntiles; ++j) {
@@ -121,15 +123,22 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         }
         tc_fence_after();
         // S = Q K^T ; Sd = Qd K^T + Q Kd^T      (K-major operands, 16 channels per instruction; one
-        // accumulator at a time)
-        auto kdesc = [&](const uint16_t *tile, int kk) { return make_smem_desc(smem_u32(tile) + (kk & 3) * 32, 16, 1024); };
+        // accumulator at a time).  Descriptors are one runtime base word plus compile-time offsets: this one
+        // thread issues every MMA of the CTA, so instructions per MMA bound the tensor throughput.
+        const uint32_t stoff = (uint32_t)((size_t)st * kBoxes * kKvTile >> 4);
+        auto qd = [&](size_t member, int kk) {
+          return base16 + (uint32_t)((member + (kk >> 2) * kQTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+        };
+        auto kd = [&](size_t member, int kk) {
+          return base16 + stoff + (uint32_t)((member + (kk >> 2) * kKvTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+        };
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss(tmem + kColS, kdesc(s.q[kk >> 2], kk), kdesc(s.k[st][kk >> 2], kk), idesc_s, kk > 0);
+          mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(offsetof(Smem, k), kk), idesc_s, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          mma_ss(tmem + kColSd, kdesc(s.tq[kk >> 2], kk), kdesc(s.k[st][kk >> 2], kk), idesc_s, kk > 0);
-          mma_ss(tmem + kColSd, kdesc(s.q[kk >> 2], kk), kdesc(s.tk[st][kk >> 2], kk), idesc_s, true);
+          mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, tq), kk), kd(offsetof(Smem, k), kk), idesc_s, kk > 0);
+          mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, q), kk), kd(offsetof(Smem, tk), kk), idesc_s, true);
         }
         tc_commit(&s.s_full);
         if (!mbar_wait(&s.p_full, j & 1)) {
@@ -140,13 +149,13 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         // O += P V ; Od' += U V + P Vd          (A from TMEM, B = value tile read MN-major, 16 keys per instruction)
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
-          const uint32_t lbo = kBN * 128;  // bytes between 64-channel column blocks of a value tile
-          const uint64_t dv = make_smem_desc(smem_u32(s.v[st][0]) + kk * 2048, lbo, 1024);
-          const uint64_t dtv = make_smem_desc(smem_u32(s.tv[st][0]) + kk * 2048, lbo, 1024);
+          // value tiles read MN-major: 16 keys = 2 KiB per step, 64-channel column blocks kBN * 128 bytes apart
+          const uint32_t dv = base16 + stoff + (uint32_t)((offsetof(Smem, v) + kk * 2048) >> 4) + desc_lo_mn_major(kBN * 128);
+          const uint32_t dtv = base16 + stoff + (uint32_t)((offsetof(Smem, tv) + kk * 2048) >> 4) + desc_lo_mn_major(kBN * 128);
           const bool acc = (j > 0) || (kk > 0);
-          mma_ts(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);
-          mma_ts(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, acc);
-          mma_ts(tmem + kColOd, tmem + kColS + kk * 8, dtv, idesc_o, true);
+          mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);
+          mma_ts_lo(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, acc);
+          mma_ts_lo(tmem + kColOd, tmem + kColS + kk * 8, dtv, idesc_o, true);
         }
         tc_commit(&s.kv_empty[st]);
         tc_commit(&s.o_done);

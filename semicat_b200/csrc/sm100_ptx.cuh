@@ -132,6 +132,31 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       : "memory");
 }
 
+// Cheap-to-issue forms.  One thread issues every MMA of a CTA, so the instructions spent per MMA bound the
+// tensor throughput: these take only the low descriptor word (start address >> 4 plus the leading-offset
+// field, which callers form as `base + compile-time constant`) and share one high word.
+//   high word: stride offset 1024 B (>> 4 = 64), descriptor version 1 (bit 14), 128-byte swizzle (2 << 29)
+constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+constexpr uint32_t kDescLoKMajor = 1u << 16;  // leading offset field for K-major tiles (unused by the hardware)
+__host__ __device__ constexpr uint32_t desc_lo_mn_major(uint32_t lbo_bytes) { return (lbo_bytes >> 4) << 16; }
+
+__device__ __forceinline__ void mma_ss_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(kDescHi)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(kDescHi)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05.ld / st  (32 lanes x 32 bit, N columns)
 // Each thread of the warp reads/writes N consecutive 32-bit columns of its own TMEM lane
 // (lane = 32 * (warp_id % 4) + lane_id; the lane field of `taddr` must be that warp's base lane).
