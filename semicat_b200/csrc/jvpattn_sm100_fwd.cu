@@ -35,10 +35,7 @@ struct FwdSmem {
   static constexpr int kBoxes = D / 64;
   alignas(1024) uint16_t q[kBoxes][kBM * 64];
   alignas(1024) uint16_t tq[kBoxes][kBM * 64];
-  alignas(1024) uint16_t k[kStages][kBoxes][kBN * 64];
-  alignas(1024) uint16_t tk[kStages][kBoxes][kBN * 64];
-  alignas(1024) uint16_t v[kStages][kBoxes][kBN * 64];
-  alignas(1024) uint16_t tv[kStages][kBoxes][kBN * 64];
+  alignas(1024) uint16_t kv[kStages][4][kBoxes][kBN * 64];  // per stage: K, Kd, V, Vd (adjacent so pairs can be one operand)
   uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full, p_full, o_done;
   uint32_t tmem_base;
 };
@@ -99,10 +96,10 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         }
         mbar_expect_tx(&s.kv_full[st], 4 * kBN * D * 2);
         for (int x = 0; x < kBoxes; ++x) {
-          tma_load_4d(s.k[st][x], &maps.k, &s.kv_full[st], 64 * x, j * kBN, h, b);
-          tma_load_4d(s.tk[st][x], &maps.tk, &s.kv_full[st], 64 * x, j * kBN, h, b);
-          tma_load_4d(s.v[st][x], &maps.v, &s.kv_full[st], 64 * x, j * kBN, h, b);
-          tma_load_4d(s.tv[st][x], &maps.tv, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.kv[st][0][x], &maps.k, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.kv[st][1][x], &maps.tk, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.kv[st][2][x], &maps.v, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          tma_load_4d(s.kv[st][3][x], &maps.tv, &s.kv_full[st], 64 * x, j * kBN, h, b);
         }
       }
     }
@@ -111,6 +108,11 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(kBM, kBN, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kBM, D, kBf16, false, true);
+      // products that share their A operand and have adjacent B tiles / accumulators go out as one instruction of
+      // twice the width (fewer instructions for the one issuing thread; N = 128 runs at the full tensor rate)
+      constexpr bool kMerge = kBoxes == 1;
+      constexpr uint32_t idesc_s2 = make_idesc(kBM, 2 * kBN, kBf16, false, false);
+      constexpr uint32_t idesc_o2 = make_idesc(kBM, 2 * D <= 256 ? 2 * D : D, kBf16, false, true);
       const uint32_t base16 = smem_u32(&s) >> 4;
       constexpr uint32_t kQTile = kBM * 128, kKvTile = kBN * 128;  // bytes of one 64-channel box
       bool ok = mbar_wait(&s.q_full, 0);
@@ -125,20 +127,27 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         // S = Q K^T ; Sd = Qd K^T + Q Kd^T      (K-major operands, 16 channels per instruction; one
         // accumulator at a time).  Descriptors are one runtime base word plus compile-time offsets: this one
         // thread issues every MMA of the CTA, so instructions per MMA bound the tensor throughput.
-        const uint32_t stoff = (uint32_t)((size_t)st * kBoxes * kKvTile >> 4);
+        const uint32_t kvlo = base16 + (uint32_t)((offsetof(Smem, kv) + (size_t)st * 4 * kBoxes * kKvTile) >> 4);
         auto qd = [&](size_t member, int kk) {
           return base16 + (uint32_t)((member + (kk >> 2) * kQTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
         };
-        auto kd = [&](size_t member, int kk) {
-          return base16 + stoff + (uint32_t)((member + (kk >> 2) * kKvTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+        auto kd = [&](int t, int kk) {
+          return kvlo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kKvTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
         };
+        if (kMerge) {
+          // [S | Sd] = Q [K ; Kd]^T in one N = 128 instruction per step, then Sd += Qd K^T
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk)
-          mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(offsetof(Smem, k), kk), idesc_s, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(0, kk), idesc_s2, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, tq), kk), kd(offsetof(Smem, k), kk), idesc_s, kk > 0);
-          mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, q), kk), kd(offsetof(Smem, tk), kk), idesc_s, true);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, tq), kk), kd(0, kk), idesc_s, true);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(0, kk), idesc_s, kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, tq), kk), kd(0, kk), idesc_s, kk > 0);
+            mma_ss_lo(tmem + kColSd, qd(offsetof(Smem, q), kk), kd(1, kk), idesc_s, true);
+          }
         }
         tc_commit(&s.s_full);
         if (!mbar_wait(&s.p_full, j & 1)) {
@@ -149,13 +158,19 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         // O += P V ; Od' += U V + P Vd          (A from TMEM, B = value tile read MN-major, 16 keys per instruction)
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
-          // value tiles read MN-major: 16 keys = 2 KiB per step, 64-channel column blocks kBN * 128 bytes apart
-          const uint32_t dv = base16 + stoff + (uint32_t)((offsetof(Smem, v) + kk * 2048) >> 4) + desc_lo_mn_major(kBN * 128);
-          const uint32_t dtv = base16 + stoff + (uint32_t)((offsetof(Smem, tv) + kk * 2048) >> 4) + desc_lo_mn_major(kBN * 128);
+          // value tiles read MN-major: 16 keys = 2 KiB per step; consecutive 64-channel column blocks (and, for
+          // D = 64, V followed by Vd) are kBN * 128 bytes apart
+          const uint32_t dv = kvlo + (uint32_t)((2 * kBoxes * kKvTile + kk * 2048) >> 4) + desc_lo_mn_major(kKvTile);
+          const uint32_t dtv = kvlo + (uint32_t)((3 * kBoxes * kKvTile + kk * 2048) >> 4) + desc_lo_mn_major(kKvTile);
           const bool acc = (j > 0) || (kk > 0);
-          mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);
-          mma_ts_lo(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, acc);
-          mma_ts_lo(tmem + kColOd, tmem + kColS + kk * 8, dtv, idesc_o, true);
+          if (kMerge) {
+            mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o2, acc);    // [O | Od'] += P [V | Vd]
+            mma_ts_lo(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, true);  // Od' += U V
+          } else {
+            mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);
+            mma_ts_lo(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, acc);
+            mma_ts_lo(tmem + kColOd, tmem + kColS + kk * 8, dtv, idesc_o, true);
+          }
         }
         tc_commit(&s.kv_empty[st]);
         tc_commit(&s.o_done);
