@@ -49,6 +49,7 @@ struct BwdSmem {
   static constexpr int kStages = 2;
   alignas(1024) uint16_t x[kXBuf][4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
+  alignas(1024) uint16_t stage_out[kBoxes == 1 ? kRows * 64 : 64];  // D = 64: one 128 x 64 output tile staged for a TMA store
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
   uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
   uint32_t tmem_base;
@@ -87,6 +88,7 @@ int sm_count() {
 
 struct BwdMaps {
   CUtensorMap x[4], y[4];
+  CUtensorMap out[4];  // dX0, dX1, dV, dVd as 128-row x 64-channel store boxes (D = 64 only)
 };
 
 struct BwdKernelArgs {
@@ -589,7 +591,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     }
     JVP_TRACE(14);
     tc_fence_after();
-    if (ok) {
+    {
       const int xr = x0 + row;
       const bool live = xr < a.Lx;
       const int cbase = half * (D / 2);
@@ -609,13 +611,52 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           }
         }
       };
-      if (kDoK) {
-        store_acc(kColK, a.out[0]);
-        if (has_t) store_acc(kColKd, a.out[1]);
-      }
-      if (kDoV) {
-        store_acc(kColV, a.out[2]);
-        if (has_t) store_acc(kColVd, a.out[3]);
+      // D = 64: accumulator -> registers -> swizzled shared tile -> one TMA store per tensor (coalesced, and rows
+      // past the end are clipped by the hardware); per-lane 16-byte global stores are far slower.  The two
+      // barriers are executed by every compute thread, whether or not its waits succeeded.
+      auto store_acc_tma = [&](uint32_t col, int which) {
+        if (ok) {
+          uint32_t r[32];
+          tmem_ld32(tlane + col + cbase, r);
+          tc_wait_ld();
+          unsigned char *tile = reinterpret_cast<unsigned char *>(s.stage_out);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+            v.y = pack2<T>(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+            v.z = pack2<T>(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+            v.w = pack2<T>(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+            *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, half * 4 + i)) = v;
+          }
+          fence_proxy_async();
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (ctid == 0 && ok) {
+          tma_store_4d(&maps.out[which], s.stage_out, 0, x0, h, b);
+          tma_store_commit();
+          tma_store_wait_read();
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");  // the staging tile may be overwritten
+      };
+      if (kBoxes == 1) {
+        if (kDoK) {
+          store_acc_tma(kColK, 0);
+          if (has_t) store_acc_tma(kColKd, 1);
+        }
+        if (kDoV) {
+          store_acc_tma(kColV, 2);
+          if (has_t) store_acc_tma(kColVd, 3);
+        }
+      } else if (ok) {
+        if (kDoK) {
+          store_acc(kColK, a.out[0]);
+          if (has_t) store_acc(kColKd, a.out[1]);
+        }
+        if (kDoV) {
+          store_acc(kColV, a.out[2]);
+          if (has_t) store_acc(kColVd, a.out[3]);
+        }
       }
       tc_fence_before();
       mbar_arrive(&s.acc_free);  // the next item may overwrite the accumulators
@@ -624,6 +665,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
    }  // items
   }
 
+  if (threadIdx.x == 64) tma_store_wait_all();  // the thread that issued the output stores
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
@@ -656,6 +698,12 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
     ka.out[0] = a.dk; ka.out[1] = a.dtk; ka.out[2] = a.dv; ka.out[3] = a.dtv;
   } else {
     ka.out[0] = a.dq; ka.out[1] = a.dtq;
+  }
+  if (D == 64) {
+    for (int t = 0; t < 4; ++t)
+      if (ka.out[t].ptr &&
+          !make_tensor_map(&maps.out[t], ka.out[t].ptr, a.dtype, a.B, a.H, Lx, D, ka.out[t].sb, ka.out[t].sh, ka.out[t].sl, kRows))
+        return cudaErrorInvalidValue;
   }
   ka.lse = a.lse; ka.mu = a.mu; ka.delta = delta; ka.dsum = dsum; ka.status = a.status;
   ka.B = a.B; ka.H = a.H; ka.Lx = Lx; ka.Ly = Ly; ka.Lq = a.Lq; ka.stat_len = a.stat_len;

@@ -42,6 +42,7 @@ struct FwdSmem {
 
 struct FwdMaps {
   CUtensorMap q, tq, k, tk, v, tv;
+  CUtensorMap o, to;  // outputs as 128-row x 64-channel store boxes
 };
 
 template <int D, typename T>
@@ -272,41 +273,51 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     }
     tc_fence_after();
     const int qrow = q0 + row;
-    const bool live = qrow < a.Lq;  // rows past len_q take part in the collective TMEM loads but store nothing
+    const bool live = qrow < a.Lq;  // rows past len_q are clipped by the TMA store
     if (ok) {
+      // Every MMA of this CTA has retired, so the Q / Qd tiles are dead: O and Od are staged over them in the
+      // 128-byte-swizzled box layout and leave through TMA stores (coalesced; per-lane global stores are far slower).
       const float inv = 1.f / l;
       const float mun = mu * inv;
-      T *op = static_cast<T *>(a.o.ptr) + a.o.offset(b, h, live ? qrow : 0);
-      T *tp = static_cast<T *>(a.to.ptr) + a.to.offset(b, h, live ? qrow : 0);
 #pragma unroll
       for (int c = 0; c < D; c += 32) {
         uint32_t ro[32], rd[32];
         tmem_ld32(tlane + kColO + c, ro);
         tmem_ld32(tlane + kColOd + c, rd);
         tc_wait_ld();
-        uint32_t po[16], pd[16];
+        unsigned char *otile = reinterpret_cast<unsigned char *>(s.q[c / 64]);
+        unsigned char *dtile = reinterpret_cast<unsigned char *>(s.tq[c / 64]);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float o0 = __uint_as_float(ro[2 * i]) * inv, o1 = __uint_as_float(ro[2 * i + 1]) * inv;
-          const float d0 = __uint_as_float(rd[2 * i]) * inv - mun * o0;
-          const float d1 = __uint_as_float(rd[2 * i + 1]) * inv - mun * o1;
-          po[i] = pack2<T>(o0, o1);
-          pd[i] = pack2<T>(d0, d1);
-        }
-        if (live) {
+        for (int i = 0; i < 4; ++i) {
+          uint32_t po[4], pd[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            reinterpret_cast<uint4 *>(op + c)[i] = make_uint4(po[4 * i], po[4 * i + 1], po[4 * i + 2], po[4 * i + 3]);
-            reinterpret_cast<uint4 *>(tp + c)[i] = make_uint4(pd[4 * i], pd[4 * i + 1], pd[4 * i + 2], pd[4 * i + 3]);
+          for (int t = 0; t < 4; ++t) {
+            const int e = 8 * i + 2 * t;
+            const float o0 = __uint_as_float(ro[e]) * inv, o1 = __uint_as_float(ro[e + 1]) * inv;
+            po[t] = pack2<T>(o0, o1);
+            pd[t] = pack2<T>(__uint_as_float(rd[e]) * inv - mun * o0, __uint_as_float(rd[e + 1]) * inv - mun * o1);
           }
+          const uint32_t off = swizzle128_offset(row, (c % 64) / 8 + i);
+          *reinterpret_cast<uint4 *>(otile + off) = make_uint4(po[0], po[1], po[2], po[3]);
+          *reinterpret_cast<uint4 *>(dtile + off) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
         }
       }
+      fence_proxy_async();
       if (live) {
         const size_t si = ((size_t)b * a.H + h) * a.stat_len + qrow;
         a.lse[si] = m * kLn2 + __logf(l);
         a.mu[si] = mun;
         if (a.li) a.li[si] = l;
       }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // all four softmax warps, whether or not their waits succeeded
+    if (threadIdx.x == 64 && ok) {
+      for (int x = 0; x < kBoxes; ++x) {
+        tma_store_4d(&maps.o, s.q[x], 64 * x, q0, h, b);
+        tma_store_4d(&maps.to, s.tq[x], 64 * x, q0, h, b);
+      }
+      tma_store_commit();
+      tma_store_wait_all();
     }
   }
 
@@ -318,10 +329,10 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
 template <int D, typename T>
 cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
   FwdMaps maps;
-  const View *views[6] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv};
-  CUtensorMap *dst[6] = {&maps.q, &maps.tq, &maps.k, &maps.tk, &maps.v, &maps.tv};
-  for (int i = 0; i < 6; ++i) {
-    const bool is_q = i < 2;
+  const View *views[8] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv, &a.o, &a.to};
+  CUtensorMap *dst[8] = {&maps.q, &maps.tq, &maps.k, &maps.tk, &maps.v, &maps.tv, &maps.o, &maps.to};
+  for (int i = 0; i < 8; ++i) {
+    const bool is_q = i < 2 || i >= 6;
     if (!make_tensor_map(dst[i], views[i]->ptr, a.dtype, a.B, a.H, is_q ? a.Lq : a.Lk, D, views[i]->sb, views[i]->sh,
                          views[i]->sl, is_q ? kBM : kBN))
       return cudaErrorInvalidValue;
