@@ -259,7 +259,7 @@ TRAIN_CONFIGS = {
 }
 
 
-def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp"):
+def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp", use_graph=True):
     """Flow-map training steps of the DiT (semicat_b200/train_step.py) on uniform random tokens: global batch
     sharded over the ranks, forward-mode JVP through every attention layer for the first `sd_prop` of each
     shard, AdamW, one flat gradient all-reduce per step.  Returns (ms per step, tokens per step, last loss)."""
@@ -269,16 +269,18 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     torch.manual_seed(1234)  # same initial weights on every rank
     net = train_step.DiT(tc["vocab"], 768, 128, 12, 12, dropout=0.1, length=tc["length"], embed_type=tc["embed"]).to(device)
     flat = ddp.FlatGradients(net.parameters())
-    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True, capturable=True)
     lo, hi = ddp.shard_bounds(tc["global_batch"], rank, world)
     gen = torch.Generator().manual_seed(99 + rank)
     host_tokens = [torch.randint(0, tc["vocab"], (hi - lo, tc["length"]), generator=gen).pin_memory() for _ in range(4)]
-    dgen = torch.Generator(device=device).manual_seed(7 + rank)
+    torch.cuda.manual_seed(7 + rank)  # per-rank noise from the default CUDA generator (graph-capturable)
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+    tok_stage = torch.empty_like(host_tokens[0]).pin_memory()  # the host refills this buffer before every step
+    x1 = torch.empty(hi - lo, tc["length"], dtype=torch.long, device=device)
 
-    def step(i):
-        x1 = host_tokens[i % 4].to(device, non_blocking=True)
-        noise = train_step.draw_noise(x1, tc["vocab"], generator=dgen)
+    def body():
+        x1.copy_(tok_stage, non_blocking=True)
+        noise = train_step.draw_noise(x1, tc["vocab"])
         flat.zero()
         vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention)
         loss = train_step.total_loss(vf, sd)
@@ -287,9 +289,42 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
         opt.step()
         loss_host.copy_(loss.detach(), non_blocking=True)
 
+    graph = None
+
+    def step(i):
+        tok_stage.copy_(host_tokens[i % 4])
+        if graph is not None:
+            graph.replay()
+        else:
+            body()
+
     for i in range(warmup):
         step(i)
     torch.cuda.synchronize()
+    mode = "eager"
+    if use_graph:
+        # The step is launch-bound on the host (thousands of small kernels under forward-mode AD), so the whole
+        # step - H2D of the tokens, noise, forward/JVP, backward, gradient all-reduce, AdamW, D2H of the loss -
+        # is captured once into a CUDA graph and replayed.
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                body()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                body()
+            graph = g
+            mode = "cuda_graph"
+            step(0)
+            torch.cuda.synchronize()
+        except Exception as e:  # pragma: no cover - depends on driver / NCCL support for capture
+            print(f"[bench] training-step graph capture unavailable ({type(e).__name__}: {str(e)[:200]}); running eagerly",
+                  file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
@@ -308,9 +343,10 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
     peak_gb = torch.cuda.max_memory_allocated() / 1e9
+    graph = None
     del net, opt, flat
     torch.cuda.empty_cache()
-    return ms, tc["global_batch"] * tc["length"], float(loss_host), peak_gb
+    return ms, tc["global_batch"] * tc["length"], float(loss_host), peak_gb, mode
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
@@ -322,7 +358,26 @@ def cpu_path(cfg, repeats, threads=None):
     return best, used
 
 
+def _claim_stdout():
+    """Libraries (NCCL among them) print banners on stdout; the contract is ONE JSON line there.  Point fd 1 at
+    stderr for the rest of the process and hand back a file object on the real stdout for the final line."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
 def main():
+    global print
+    _out = _claim_stdout()
+    _print = print
+
+    def print(*a, **kw):  # noqa: A001 - route only this module's prints
+        if "file" in kw:
+            return _print(*a, **kw)
+        _print(*a, file=_out, **kw)
+        _out.flush()
+
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -481,10 +536,10 @@ def main():
         try:
             sets = host_sets = None  # release the attention buffers before the model is built
             torch.cuda.empty_cache()
-            tms, tokens, tloss, peak_gb = run_train("dit_lm1b", 3, 2, device, rank, world, dist, sampler, sd_prop=0.25)
+            tms, tokens, tloss, peak_gb, tmode = run_train("dit_lm1b", 3, 3, device, rank, world, dist, sampler, sd_prop=0.25)
             line["train"] = {"workload": "DiT 12x768, 12 heads, vocab 30522, seq 128, global batch 512, sd_prop 0.25 (lag), "
                                          "bf16 autocast, AdamW, uniform random tokens", "scaling": "strong",
-                             "ms_per_step": tms, "tokens_per_s": tokens / (tms * 1e-3), "steps": 3, "loss": tloss,
+                             "ms_per_step": tms, "tokens_per_s": tokens / (tms * 1e-3), "steps": 3, "loss": tloss, "launch": tmode,
                              "peak_mem_gb": peak_gb}
         except Exception as e:  # the attention line above stands on its own
             line["train"] = {"error": f"{type(e).__name__}: {e}"[:300]}
@@ -508,8 +563,8 @@ def main_train(args):
     dist = dist_mod if world > 1 else None
     sampler = ClockSampler(local_rank)
     launches0 = _lib.launch_count()
-    ms, tokens, loss, peak_gb = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist, sampler,
-                                          sd_prop=args.sd_prop)
+    ms, tokens, loss, peak_gb, mode = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist,
+                                                sampler, sd_prop=args.sd_prop, use_graph=not args.profile_mode)
     launched = _lib.launch_count() - launches0
     tc = TRAIN_CONFIGS[args.workload]
     if rank == 0:
@@ -520,7 +575,7 @@ def main_train(args):
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{args.workload}: DiT 12x768/12 heads, vocab {tc['vocab']}, seq {tc['length']}, global batch "
                                    f"{tc['global_batch']}, sd_prop {args.sd_prop} (lag), AdamW", "parallelism": f"dp{world}",
-                       "l2": "activations per step far exceed the 126 MB L2"},
+                       "l2": "activations per step far exceed the 126 MB L2", "launch": mode},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 8 // world, "d2h_bytes_per_step": 4,
                     "note": "token ids come from pinned host memory and the loss goes back to the host every step"},
             "gpu_launches": int(launched), "loss": loss, "peak_mem_gb": peak_gb, "clocks": sampler.summary(),
