@@ -218,20 +218,34 @@ def run_e2e(cfg, host_sets, steps, warmup, device, dist, sampler):
     from semicat_b200 import sdpa_jvp
     pinned = [{n: x.pin_memory() for n, x in hs.items()} for hs in host_sets]
     B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
-    out_host = [torch.empty(B, H, L, D, dtype=torch.bfloat16).pin_memory() for _ in range(8)]
+    # two steps in flight on two streams, so one step's result copy overlaps the next step's input copy
+    # (PCIe is full duplex); each stream has its own pinned result buffers
+    streams = [torch.cuda.Stream(device=device) for _ in range(2)]
+    out_host = [[torch.empty(B, H, L, D, dtype=torch.bfloat16).pin_memory() for _ in range(8)] for _ in range(2)]
     names = ("q", "k", "v", "tq", "tk", "tv")
 
     def step(i):
         src = pinned[i % len(pinned)]
-        dev = {n: x.to(device, non_blocking=True) for n, x in src.items()}
-        leaves = [dev[n].transpose(1, 2).requires_grad_(True) for n in names]
-        o, to = torch.func.jvp(sdpa_jvp, tuple(leaves[:3]), tuple(leaves[3:]))
-        grads = torch.autograd.grad([o, to], leaves, [dev["g_o"].transpose(1, 2), dev["g_to"].transpose(1, 2)])
-        for dst, src_t in zip(out_host, (o.detach(), to.detach(), *grads)):
-            dst.copy_(src_t, non_blocking=True)
+        with torch.cuda.stream(streams[i % 2]):
+            dev = {n: x.to(device, non_blocking=True) for n, x in src.items()}
+            leaves = [dev[n].transpose(1, 2).requires_grad_(True) for n in names]
+            o, to = torch.func.jvp(sdpa_jvp, tuple(leaves[:3]), tuple(leaves[3:]))
+            grads = torch.autograd.grad([o, to], leaves, [dev["g_o"].transpose(1, 2), dev["g_to"].transpose(1, 2)])
+            for dst, src_t in zip(out_host[i % 2], (o.detach(), to.detach(), *grads)):
+                dst.copy_(src_t, non_blocking=True)
 
+    def fork():
+        for st in streams:
+            st.wait_stream(torch.cuda.current_stream())
+
+    def join():
+        for st in streams:
+            torch.cuda.current_stream().wait_stream(st)
+
+    fork()
     for i in range(max(warmup, 3)):
         step(i)
+    join()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
@@ -239,8 +253,10 @@ def run_e2e(cfg, host_sets, steps, warmup, device, dist, sampler):
     with sampler:
         t0 = time.perf_counter()
         start.record()
+        fork()
         for i in range(steps):
             step(i)
+        join()
         end.record()
         end.synchronize()
         wall_ms = (time.perf_counter() - t0) * 1e3
@@ -472,7 +488,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "api": "sdpa_jvp under torch.func.jvp + torch.autograd.grad, pinned host buffers"},
+                "steps": e2e_steps, "api": "sdpa_jvp under torch.func.jvp + torch.autograd.grad, pinned host buffers, two steps in flight on two streams"},
         "gpu_launches": int(launched),
     }
 
