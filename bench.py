@@ -399,7 +399,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS))
+    ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS) + ["sweep5"])
     ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
@@ -407,6 +407,8 @@ def main():
     args = ap.parse_args()
     if args.workload in TRAIN_CONFIGS:
         return main_train(args)
+    if args.workload == "sweep5":
+        return main_sweep(args)
     cfg = WORKLOADS[args.workload]
     B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
     rank = int(os.environ.get("RANK", "0"))
@@ -565,6 +567,34 @@ def main():
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def main_sweep(args):
+    """`--workload sweep5`: BASELINE config 5, the long-sequence sweep (H=16, d in {64,128}, L in {1024..8192},
+    B*L = 65536, N(0,1) primals and tangents), fused fwd+bwd TFLOP/s per shape on one GPU.  One JSON line."""
+    import torch
+    from semicat_b200 import _lib
+    _lib.load()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    pk = peaks()
+    rows = []
+    for D in (64, 128):
+        for L in (1024, 2048, 4096, 8192):
+            cfg = dict(B=65536 // L, H=16, L=L, D=D, q_scale=1.0, t_scale=1.0)
+            sets = [DeviceSet(host_inputs(cfg, seed=i), device) for i in range(2)]
+            ms, _, _ = run_device(cfg, sets, max(2, min(args.steps, 6)), 3, None, ClockSampler(0), use_graph=False)
+            prof = run_profile(sets, 2)
+            steps = max(2, min(args.steps, 6))
+            fl = flops_per_step(cfg["B"], 16, L, D)
+            tf = fl / (ms / steps * 1e-3) / 1e12
+            rows.append({"L": L, "d": D, "B": cfg["B"], "ms_per_step": ms / steps, "tflops": tf,
+                         "frac_of_bf16_peak": tf / pk["bf16_tflops"],
+                         "kernel_ms": {k_: v_[0] / v_[1] for k_, v_ in prof.items()}})
+            del sets
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "jvp_attn_fwd_bwd_tflops", "unit": "TFLOP/s", "workload": "config 5 sweep, bf16, H16, B*L=65536",
+                      "peak": pk, "sweep": rows}))
 
 
 def main_train(args):
