@@ -39,6 +39,10 @@ WORKLOADS = {
     "L2048_d128_small": dict(B=2, H=16, L=2048, D=128, q_scale=1.0, t_scale=1.0),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload
+# (profiles/config2_launch_list_and_counters.md); None where no capture exists
+NCU_TRAFFIC = {"config2": {"sm100_bwd_kernel<key owner>": 116.4e6, "sm100_bwd_kernel<query owner>": 109.1e6,
+                           "sm100_fwd_kernel": 80.3e6}}
 
 
 def flops_per_step(B, H, L, D):
@@ -521,7 +525,8 @@ def main():
         top = kernels[0]
         if bound == "hbm":
             line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gb_s"], "peak": pk["hbm_gbs"],
-                                "unit": "GB/s", "frac": top["gb_s"] / pk["hbm_gbs"], "traffic": None,
+                                "unit": "GB/s", "frac": top["gb_s"] / pk["hbm_gbs"],
+                                "traffic": NCU_TRAFFIC.get(args.workload, {}).get(top["kernel"]),
                                 "peak_source": pk["source"]}
         else:
             line["roofline"] = {"bound": "tensor", "kernel": top["kernel"], "achieved": top["executed_tflops"],
