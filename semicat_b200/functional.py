@@ -90,7 +90,10 @@ class _Attention(torch.autograd.Function):
     @staticmethod
     def forward(q, k, v):
         B, H, S, _ = q.shape
-        y = torch.empty((B, H, S, v.shape[-1]), dtype=q.dtype, device=q.device)
+        # (B, H, S, D) view of (B, S, H, D)-contiguous memory: the layout the denoiser wants back
+        # (duo.py:154-155 reshapes the (B, S, H, D) result to (B, S, H*D)), so that reshape stays a view.
+        # The reference hands out a (B, H, S, D)-contiguous buffer and pays a copy there; shapes are the same.
+        y = torch.empty((B, S, H, v.shape[-1]), dtype=q.dtype, device=q.device).transpose(1, 2)
         # same placeholder value as the reference (log of the key count), overwritten by the kernel
         lse = torch.full((B, H, ops.stat_len(S)), math.log(max(k.shape[-2], 1)), dtype=torch.float32, device=q.device)
         return y, lse
