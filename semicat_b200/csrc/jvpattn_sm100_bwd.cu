@@ -49,7 +49,6 @@ struct BwdSmem {
   static constexpr int kStages = 2;
   alignas(1024) uint16_t x[kXBuf][4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
-  alignas(1024) uint16_t stage_out[kBoxes == 1 ? kRows * 64 : 64];  // D = 64: one 128 x 64 output tile staged for a TMA store
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
   uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
   uint32_t tmem_base;
@@ -190,7 +189,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   if (threadIdx.x == 0) {
     for (int i = 0; i < kXBuf; ++i) {
       mbar_init(&s.x_full[i], 1);
-      mbar_init(&s.x_empty[i], 1);
+      mbar_init(&s.x_empty[i], kBoxes == 1 ? 2 : 1);  // MMA issuer, plus the thread whose output stores read the buffer
     }
     mbar_init(&s.acc_free, kComputeThreads);
     for (int i = 0; i < kStages; ++i) {
@@ -467,20 +466,22 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     };
     float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
     if (kKV && blockIdx.x < items) pre = fetch_stat(blockIdx.x, 0);
+    // per-row statistics of the query owner, {lse * log2e, mu, delta, dsum}, fetched one item ahead
+    auto fetch_row_stat = [&](int it_) -> float4 {
+      int bb, hh, xx;
+      decode(it_, bb, hh, xx);
+      if (kKV || it_ >= items || xx + row >= a.Lx) return make_float4(INFINITY, 0.f, 0.f, 0.f);
+      const size_t si = ((size_t)bb * a.H + hh) * a.stat_len + xx + row;
+      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
+    };
+    float4 rstat_next = fetch_row_stat(blockIdx.x);
     bool ok = true;
     int n = 0, g = 0;
+    int pending_xb = -1;  // compute thread 0: X buffer whose output stores have been issued but not yet released
    for (int it = blockIdx.x; it < items; it += gridDim.x, ++n) {
     int b, h, x0;
     decode(it, b, h, x0);
-    const size_t stat_base = ((size_t)b * a.H + h) * a.stat_len;
-    // per-row statistics of the query owner: {lse * log2e, mu, delta, dsum}
-    float4 rstat = make_float4(INFINITY, 0.f, 0.f, 0.f);
-    if (!kKV && x0 + row < a.Lx) {
-      rstat.x = a.lse[stat_base + x0 + row] * kLog2e;
-      rstat.y = has_t ? a.mu[stat_base + x0 + row] : 0.f;
-      rstat.z = a.delta[stat_base + x0 + row];
-      rstat.w = a.dsum[stat_base + x0 + row];
-    }
+    const float4 rstat = rstat_next;
     for (int j = 0; j < ntiles; ++j, ++g) {
       if (kKV) {
         if (ctid < TILE) s.stats[g & 1][ctid] = pre;
@@ -544,6 +545,12 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       tc_fence_before();
       mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
       JVP_TRACE(11);
+      if (pending_xb >= 0) {
+        // the previous item's output stores have long finished reading its X buffer: hand it back to the producer
+        tma_store_wait_read();
+        mbar_arrive(&s.x_empty[pending_xb]);
+        pending_xb = -1;
+      }
       if (!kDoK) continue;
       // ---- second half: W1 = scale P (A - delta), W2 = scale P ((A - delta) N + C - dsum)
       if (!__all_sync(0xffffffffu, mbar_wait(&s.s2_full, g & 1))) {
@@ -611,42 +618,46 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           }
         }
       };
-      // D = 64: accumulator -> registers -> swizzled shared tile -> one TMA store per tensor (coalesced, and rows
-      // past the end are clipped by the hardware); per-lane 16-byte global stores are far slower.  The two
-      // barriers are executed by every compute thread, whether or not its waits succeeded.
-      auto store_acc_tma = [&](uint32_t col, int which) {
-        if (ok) {
-          uint32_t r[32];
-          tmem_ld32(tlane + col + cbase, r);
-          tc_wait_ld();
-          unsigned char *tile = reinterpret_cast<unsigned char *>(s.stage_out);
+      // D = 64: accumulators -> registers -> swizzled shared tiles -> one TMA store per tensor (coalesced, and rows
+      // past the end are clipped by the hardware); per-lane 16-byte global stores are far slower.  The item's own
+      // X tiles are dead by now (every MMA of the item has retired), so they serve as the staging tiles; the buffer
+      // goes back to the producer only after the stores have read it (see `pending_xb`).  The barrier is executed
+      // by every compute thread, whether or not its waits succeeded.
+      const int xb = n % kXBuf;
+      auto stage_acc = [&](uint32_t col, int which) {
+        uint32_t r[32];
+        tmem_ld32(tlane + col + cbase, r);
+        tc_wait_ld();
+        unsigned char *tile = reinterpret_cast<unsigned char *>(s.x[xb][which][0]);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 v;
-            v.x = pack2<T>(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-            v.y = pack2<T>(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-            v.z = pack2<T>(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-            v.w = pack2<T>(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-            *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, half * 4 + i)) = v;
-          }
+        for (int i = 0; i < 4; ++i) {
+          uint4 v;
+          v.x = pack2<T>(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+          v.y = pack2<T>(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+          v.z = pack2<T>(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+          v.w = pack2<T>(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+          *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, half * 4 + i)) = v;
+        }
+      };
+      if (kBoxes == 1) {
+        const bool w0 = kDoK, w1 = kDoK && has_t, w2 = kDoV, w3 = kDoV && has_t;
+        if (ok) {
+          if (w0) stage_acc(kColK, 0);
+          if (w1) stage_acc(kColKd, 1);
+          if (w2) stage_acc(kColV, 2);
+          if (w3) stage_acc(kColVd, 3);
           fence_proxy_async();
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");
-        if (ctid == 0 && ok) {
-          tma_store_4d(&maps.out[which], s.stage_out, 0, x0, h, b);
-          tma_store_commit();
-          tma_store_wait_read();
-        }
-        asm volatile("bar.sync 2, 256;" ::: "memory");  // the staging tile may be overwritten
-      };
-      if (kBoxes == 1) {
-        if (kDoK) {
-          store_acc_tma(kColK, 0);
-          if (has_t) store_acc_tma(kColKd, 1);
-        }
-        if (kDoV) {
-          store_acc_tma(kColV, 2);
-          if (has_t) store_acc_tma(kColVd, 3);
+        if (ctid == 0) {
+          if (ok) {
+            if (w0) tma_store_4d(&maps.out[0], s.x[xb][0][0], 0, x0, h, b);
+            if (w1) tma_store_4d(&maps.out[1], s.x[xb][1][0], 0, x0, h, b);
+            if (w2) tma_store_4d(&maps.out[2], s.x[xb][2][0], 0, x0, h, b);
+            if (w3) tma_store_4d(&maps.out[3], s.x[xb][3][0], 0, x0, h, b);
+            tma_store_commit();
+          }
+          pending_xb = xb;
         }
       } else if (ok) {
         if (kDoK) {
@@ -658,6 +669,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           if (has_t) store_acc(kColVd, a.out[3]);
         }
       }
+      rstat_next = fetch_row_stat(it + gridDim.x);
       tc_fence_before();
       mbar_arrive(&s.acc_free);  // the next item may overwrite the accumulators
       JVP_TRACE(15);
@@ -665,7 +677,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
    }  // items
   }
 
-  if (threadIdx.x == 64) tma_store_wait_all();  // the thread that issued the output stores
+  if (threadIdx.x == 64) tma_store_wait_all();  // the thread that issued the output stores (nobody waits on x_empty any more)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
