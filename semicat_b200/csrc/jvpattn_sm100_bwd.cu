@@ -219,18 +219,49 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       prefetch_tensormap(&maps.y[0]);
       int n = 0, g = 0;
       bool ok = true;
-      for (int it = blockIdx.x; ok && it < items; it += gridDim.x, ++n) {
+      // owned-row tiles of work item `it_` (the n_-th of this CTA) into X buffer n_ % kXBuf
+      auto load_x = [&](int it_, int n_) -> bool {
         int b, h, x0;
-        decode(it, b, h, x0);
-        const int xb = n % kXBuf;
-        if (!mbar_wait(&s.x_empty[xb], ((n / kXBuf) & 1) ^ 1)) {
+        decode(it_, b, h, x0);
+        const int xb = n_ % kXBuf;
+        if (!mbar_wait(&s.x_empty[xb], ((n_ / kXBuf) & 1) ^ 1)) {
           atomicExch(a.status, 209u);
-          break;
+          return false;
         }
         mbar_expect_tx(&s.x_full[xb], __popc(a.xmask) * kRows * D * 2);
         for (int t = 0; t < 4; ++t)
           if (a.xmask >> t & 1)
             for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[xb][t][x], &maps.x[t], &s.x_full[xb], 64 * x, x0, h, b);
+        if (kXBuf == 1 && it_ + (int)gridDim.x < items) {  // single X buffer: at least bring the next item's rows into L2
+          decode(it_ + gridDim.x, b, h, x0);
+          for (int t = 0; t < 4; ++t)
+            if (a.xmask >> t & 1)
+              for (int x = 0; x < kBoxes; ++x) tma_prefetch_4d(&maps.x[t], 64 * x, x0, h, b);
+        }
+        return true;
+      };
+      // A streamed tile can only be requested once its stage is free, one tile ahead at best, which is less
+      // than the DRAM latency when an item has few tiles: the tile `kAhead` positions further down this CTA's
+      // stream is therefore pulled into L2 when a tile is requested.
+      constexpr int kAhead = 2;
+      auto prefetch_y = [&](int n_, int j_) {
+        const int pos = j_ + kAhead;
+        const int it_ = blockIdx.x + (n_ + pos / ntiles) * (int)gridDim.x;
+        if (it_ >= items) return;
+        int b, h, x0;
+        decode(it_, b, h, x0);
+        for (int t = 0; t < 4; ++t)
+          if (a.ymask >> t & 1)
+            for (int x = 0; x < kBoxes; ++x) tma_prefetch_4d(&maps.y[t], 64 * x, (pos % ntiles) * TILE, h, b);
+      };
+      // With two X buffers the next item's rows are requested as soon as this item's first two streamed tiles
+      // are on their way, so they are resident long before the item starts.
+      const int jx = kXBuf == 2 ? (ntiles < 2 ? ntiles - 1 : 1) : -1;
+      if (blockIdx.x < items) ok = load_x(blockIdx.x, 0);
+      for (int it = blockIdx.x; ok && it < items; it += gridDim.x, ++n) {
+        int b, h, x0;
+        decode(it, b, h, x0);
+        if (kXBuf == 1 && n > 0 && !(ok = load_x(it, n))) break;
         for (int j = 0; j < ntiles; ++j, ++g) {
           const int st = g % kStages;
           if (!mbar_wait(&s.y_empty[st], ((g / kStages) & 1) ^ 1)) {
@@ -242,6 +273,8 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           for (int t = 0; t < 4; ++t)
             if (a.ymask >> t & 1)
               for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][t][x], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
+          prefetch_y(n, j);
+          if (j == jx && it + (int)gridDim.x < items && !(ok = load_x(it + gridDim.x, n + 1))) break;
         }
       }
     }
