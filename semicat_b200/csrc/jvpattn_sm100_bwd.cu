@@ -56,11 +56,11 @@ struct BwdSmem {
 
 // Optional event trace of CTA 0 (debug builds only: -DJVPATTN_TRACE): (tag, clock64) pairs.
 #ifdef JVPATTN_TRACE
-__device__ unsigned long long g_trace[2][2][4096];  // [query | key owner][MMA thread | compute thread 0][event]
+__device__ unsigned long long g_trace[2][9][1024];  // [query | key owner][MMA thread | lane 0 of each compute warp][event]
 #define JVP_TRACE_DECL(role) unsigned trace_n_ = 0; const int trace_role_ = (role)
 #define JVP_TRACE(tag)                                                                                        \
   do {                                                                                                        \
-    if (blockIdx.x == 0 && trace_n_ < 4096)                                                                   \
+    if (blockIdx.x == 0 && trace_n_ < 1024)                                                                   \
       g_trace[kKV ? 1 : 0][trace_role_][trace_n_++] = ((unsigned long long)(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
   } while (0)
 #else
@@ -481,8 +481,8 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     const int col0 = half * CH;
     const int ctid = threadIdx.x - 64;  // 0..255 among the compute threads
 #ifdef JVPATTN_TRACE
-    unsigned trace_n_ = ctid == 0 ? 0u : 4096u;  // only compute thread 0 records
-    const int trace_role_ = 1;
+    unsigned trace_n_ = lane == 0 ? 0u : 1024u;  // lane 0 of each compute warp records
+    const int trace_role_ = warp - 1;
 #endif
     const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
     const float sl2 = a.scale * kLog2e;
@@ -495,7 +495,9 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       const int col = j_ * TILE + ctid;
       if (ctid >= TILE || col >= a.Lq) return make_float4(INFINITY, 0.f, 0.f, 0.f);  // padded query: P = 0
       const size_t si = ((size_t)bb * a.H + hh) * a.stat_len + col;
-      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
+      // raw values: nothing may depend on these loads until they are published a tile later (a dependent
+      // instruction here would stall the warp, and with it the barrier below, for the full memory latency)
+      return make_float4(a.lse[si], has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
     };
     float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
     if (kKV && blockIdx.x < items) pre = fetch_stat(blockIdx.x, 0);
@@ -505,7 +507,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       decode(it_, bb, hh, xx);
       if (kKV || it_ >= items || xx + row >= a.Lx) return make_float4(INFINITY, 0.f, 0.f, 0.f);
       const size_t si = ((size_t)bb * a.H + hh) * a.stat_len + xx + row;
-      return make_float4(a.lse[si] * kLog2e, has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);
+      return make_float4(a.lse[si], has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);  // raw: scaled at the item's start
     };
     float4 rstat_next = fetch_row_stat(blockIdx.x);
     bool ok = true;
@@ -514,10 +516,12 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
    for (int it = blockIdx.x; it < items; it += gridDim.x, ++n) {
     int b, h, x0;
     decode(it, b, h, x0);
-    const float4 rstat = rstat_next;
+    const float4 rstat = make_float4(rstat_next.x * kLog2e, rstat_next.y, rstat_next.z, rstat_next.w);
+    // the next item's statistics are requested now and first touched at the top of the next item
+    rstat_next = fetch_row_stat(it + gridDim.x);
     for (int j = 0; j < ntiles; ++j, ++g) {
       if (kKV) {
-        if (ctid < TILE) s.stats[g & 1][ctid] = pre;
+        if (ctid < TILE) s.stats[g & 1][ctid] = make_float4(pre.x * kLog2e, pre.y, pre.z, pre.w);
         if (j + 1 < ntiles) pre = fetch_stat(it, j + 1);
         else if (it + (int)gridDim.x < items) pre = fetch_stat(it + gridDim.x, 0);
         asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -702,7 +706,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           if (has_t) store_acc(kColVd, a.out[3]);
         }
       }
-      rstat_next = fetch_row_stat(it + gridDim.x);
       tc_fence_before();
       mbar_arrive(&s.acc_free);  // the next item may overwrite the accumulators
       JVP_TRACE(15);
@@ -809,7 +812,7 @@ extern "C" int jvpattn_trace_read(unsigned long long *host) {
   cudaDeviceSynchronize();
   cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
   cudaMemset(nullptr, 0, 0);
-  static unsigned long long zeros[2][2][4096];
+  static unsigned long long zeros[2][9][1024];
   cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
   return 0;
 }
