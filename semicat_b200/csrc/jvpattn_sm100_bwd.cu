@@ -50,6 +50,11 @@ struct BwdSmem {
   alignas(1024) uint16_t x[kXBuf][4][kBoxes][kRows * 64];
   alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
+  // Query owner: the owned rows' statistics {lse, mu, delta, dsum} as four float arrays, brought in by bulk copies
+  // that complete on the same barrier as the rows.  Its compute warps then issue no global loads at all: a load in
+  // flight holds a scoreboard slot that the tensor-memory reads of the score algebra also wait on, which exposed
+  // the memory latency once per item even with nothing depending on the load.
+  alignas(16) float xstat[kXBuf][4][kRows];
   uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
   uint32_t tmem_base;
 };
@@ -228,10 +233,17 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           atomicExch(a.status, 209u);
           return false;
         }
-        mbar_expect_tx(&s.x_full[xb], __popc(a.xmask) * kRows * D * 2);
+        mbar_expect_tx(&s.x_full[xb], __popc(a.xmask) * kRows * D * 2 + (kKV ? 0 : (has_t ? 4 : 3) * kRows * 4));
         for (int t = 0; t < 4; ++t)
           if (a.xmask >> t & 1)
             for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[xb][t][x], &maps.x[t], &s.x_full[xb], 64 * x, x0, h, b);
+        if (!kKV) {
+          const size_t si = ((size_t)b * a.H + h) * a.stat_len + x0;  // stat_len is a multiple of 128: always in bounds
+          bulk_load_1d(s.xstat[xb][0], a.lse + si, kRows * 4, &s.x_full[xb]);
+          if (has_t) bulk_load_1d(s.xstat[xb][1], a.mu + si, kRows * 4, &s.x_full[xb]);
+          bulk_load_1d(s.xstat[xb][2], a.delta + si, kRows * 4, &s.x_full[xb]);
+          bulk_load_1d(s.xstat[xb][3], a.dsum + si, kRows * 4, &s.x_full[xb]);
+        }
         if (kXBuf == 1 && it_ + (int)gridDim.x < items) {  // single X buffer: at least bring the next item's rows into L2
           decode(it_ + gridDim.x, b, h, x0);
           for (int t = 0; t < 4; ++t)
@@ -501,24 +513,24 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     };
     float4 pre = make_float4(0.f, 0.f, 0.f, 0.f);
     if (kKV && blockIdx.x < items) pre = fetch_stat(blockIdx.x, 0);
-    // per-row statistics of the query owner, {lse * log2e, mu, delta, dsum}, fetched one item ahead
-    auto fetch_row_stat = [&](int it_) -> float4 {
-      int bb, hh, xx;
-      decode(it_, bb, hh, xx);
-      if (kKV || it_ >= items || xx + row >= a.Lx) return make_float4(INFINITY, 0.f, 0.f, 0.f);
-      const size_t si = ((size_t)bb * a.H + hh) * a.stat_len + xx + row;
-      return make_float4(a.lse[si], has_t ? a.mu[si] : 0.f, a.delta[si], a.dsum[si]);  // raw: scaled at the item's start
-    };
-    float4 rstat_next = fetch_row_stat(blockIdx.x);
     bool ok = true;
     int n = 0, g = 0;
     int pending_xb = -1;  // compute thread 0: X buffer whose output stores have been issued but not yet released
    for (int it = blockIdx.x; it < items; it += gridDim.x, ++n) {
     int b, h, x0;
     decode(it, b, h, x0);
-    const float4 rstat = make_float4(rstat_next.x * kLog2e, rstat_next.y, rstat_next.z, rstat_next.w);
-    // the next item's statistics are requested now and first touched at the top of the next item
-    rstat_next = fetch_row_stat(it + gridDim.x);
+    // query owner: this thread's row statistics {lse * log2e, mu, delta, dsum}, delivered with the item's rows
+    float4 rstat = make_float4(INFINITY, 0.f, 0.f, 0.f);  // row past the end: P = 0
+    if (!kKV) {
+      const int xb_ = n % kXBuf;
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.x_full[xb_], (n / kXBuf) & 1))) {
+        atomicExch(a.status, 211u);
+        ok = false;
+      }
+      if (ok && x0 + row < a.Lx)
+        rstat = make_float4(s.xstat[xb_][0][row] * kLog2e, has_t ? s.xstat[xb_][1][row] : 0.f, s.xstat[xb_][2][row],
+                            s.xstat[xb_][3][row]);
+    }
     for (int j = 0; j < ntiles; ++j, ++g) {
       if (kKV) {
         if (ctid < TILE) s.stats[g & 1][ctid] = make_float4(pre.x * kLog2e, pre.y, pre.z, pre.w);
@@ -831,6 +843,9 @@ bool sm100_bwd_supported(const BwdArgs &a) {
       if (!tma_view_ok(*v, a.D)) return false;
   }
   if (has_o && !tma_view_ok(a.g_o, a.D)) return false;
+  // the query owner's row statistics travel by 16-byte-granular bulk copies
+  if (reinterpret_cast<uintptr_t>(a.lse) % 16 || reinterpret_cast<uintptr_t>(a.workspace) % 16 || a.stat_len % 4) return false;
+  if (has_t && reinterpret_cast<uintptr_t>(a.mu) % 16) return false;
   return true;
 }
 

@@ -55,6 +55,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------- TMA (no multicast anywhere)
+// Contiguous global -> shared copy that completes on an mbarrier (both addresses 16-byte aligned, size a
+// multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // Pull one box of a 4-d tensor into L2 (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *map, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2),
