@@ -67,6 +67,24 @@ struct LaunchScope {
   void *slot_;
 };
 
+// Launch with the programmatic-serialization attribute: the kernel may start as soon as the kernel before it in
+// the stream has released its dependents (see griddep_launch_dependents), without waiting for it to finish.
+template <typename... Params, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 template <typename T> struct Elem;
 template <> struct Elem<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 x) { return __bfloat162float(x); }

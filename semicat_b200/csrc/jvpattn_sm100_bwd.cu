@@ -216,6 +216,13 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
+  // The key-owner launches read nothing that the query-owner launch writes, so they need not wait for it: the
+  // query owner (launched normally, i.e. after the row dots and everything earlier in the stream have completed)
+  // releases its dependents at once, and the key-owner CTAs, launched with the programmatic-serialization
+  // attribute, move onto SMs as the query-owner CTAs leave them.  That hides their launch and first loads and
+  // fills the tail in which only some SMs still hold a query-owner item.
+  if (!kKV) griddep_wait();
+  griddep_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -776,9 +783,10 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
   dim3 grid((unsigned)std::min<int64_t>(items, sm_count()));  // persistent: one CTA per SM walks the items
   {
     LaunchScope scope(kKV ? kIdBwdKeyTc : kIdBwdQueryTc, stream);
-    kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
+    if (kKV) e = launch_overlapped(kernel, grid, dim3(kThreads), smem, stream, maps, ka);
+    else kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
   }
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <int D, typename T>

@@ -55,6 +55,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 }
 
 // ---------------------------------------------------------------- TMA (no multicast anywhere)
+// Programmatic dependent launch.  `griddep_launch_dependents` allows a kernel that follows in the stream and was
+// launched with the programmatic-serialization attribute to start as soon as every CTA of this grid has executed
+// it (or exited); `griddep_wait` blocks until the kernel before this one has completed and its memory is visible
+// (it returns at once in a kernel that was launched normally, whose predecessor has completed by then anyway).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Contiguous global -> shared copy that completes on an mbarrier (both addresses 16-byte aligned, size a
 // multiple of 16 bytes).
 __device__ __forceinline__ void bulk_load_1d(void *smem_dst, const void *gsrc, uint32_t bytes, uint64_t *bar) {
