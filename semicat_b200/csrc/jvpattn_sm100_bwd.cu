@@ -433,7 +433,17 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         tc_fence_after();
         const uint32_t ylo_out = ybase(st);
-        if (kDoV) {
+        // (the common case, both cotangents present, is issued as straight-line code: a run-time condition between
+        //  two instructions of a group costs this thread tens of cycles per instruction)
+        if (kDoV && kMerge && has_t && has_o) {
+          const bool acc = j > 0;
+#pragma unroll
+          for (int kk = 0; kk < TILE / 16; ++kk) {
+            mma_ts_lo(tmem + kColVd, tmem + kColS + oa(kk), yb(ylo_out, 2, kk), idesc_o2, acc || kk > 0);  // [dVd | dV] += P [G | gO]
+            mma_ts_lo(tmem + kColV, tmem + kColSd + oa(kk), yb(ylo_out, 2, kk), idesc_o, true);          // dV += (P o N) G
+          }
+          initv = initvd = true;
+        } else if (kDoV) {
 #pragma unroll
           for (int kk = 0; kk < TILE / 16; ++kk) {
             if (kMerge && has_t && has_o) {
@@ -470,6 +480,15 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           }
           JVP_TRACE(4);
           tc_fence_after();
+          if (kMerge && has_t) {
+            const bool acc = j > 0;
+#pragma unroll
+            for (int kk = 0; kk < TILE / 16; ++kk) {
+              mma_ts_lo(tmem + kColKd, tmem + kColA + oa(kk), yb(ylo_out, 0, kk), idesc_o2, acc || kk > 0);  // [dX1 | dX0] += W1 [Y0 | Y1]
+              mma_ts_lo(tmem + kColK, tmem + kColC + oa(kk), yb(ylo_out, 0, kk), idesc_o, true);          // dX0 += W2 Y0
+            }
+            init0 = init1 = true;
+          } else
 #pragma unroll
           for (int kk = 0; kk < TILE / 16; ++kk) {
             if (kMerge && has_t) {
