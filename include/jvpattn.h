@@ -89,7 +89,10 @@ size_t jvpattn_bwd_workspace_bytes(const jvpattn_problem *p);
  * Either cotangent may be NULL (treated as zero) but not both.  dq, dk, dv are always written.
  * tq, tk, tv, to, mu, dtq, dtk, dtv are required when g_to is given; when it is NULL they are ignored
  * (may be NULL) and no tangent gradient is written.
- * `workspace` need not be initialised. */
+ * `workspace` need not be initialised.
+ * The call issues several kernels on `stream`; those of them that do not depend on each other run
+ * concurrently (the kernels that write dk / dv beside the one that writes dq), so no output tensor may
+ * overlap an input tensor or another output.  Work enqueued on the stream after the call sees all results. */
 int jvpattn_bwd(const jvpattn_problem *p,
                 const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
                 const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
