@@ -48,7 +48,9 @@ struct BwdSmem {
   static constexpr int kXBuf = D == 64 ? 2 : 1;  // owned-row tiles are double buffered where shared memory allows
   static constexpr int kStages = 2;
   alignas(1024) uint16_t x[kXBuf][4][kBoxes][kRows * 64];
-  alignas(1024) uint16_t y[kStages][4][kBoxes][TILE * 64];
+  // streamed tiles, 64-channel box outermost: within a box the four tensors are adjacent, so that [Y0 ; Y1] and
+  // [Y2 ; Y3] are each one K-major B operand of 2 TILE rows (merged score products) at any head dimension
+  alignas(1024) uint16_t y[kStages][kBoxes][4][TILE * 64];
   float4 stats[2][TILE];  // key owner only: per query column {lse*log2e, mu, delta, dsum} (double buffered)
   // Query owner: the owned rows' statistics {lse, mu, delta, dsum} as four float arrays, brought in by bulk copies
   // that complete on the same barrier as the rows.  Its compute warps then issue no global loads at all: a load in
@@ -291,7 +293,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           mbar_expect_tx(&s.y_full[st], __popc(a.ymask) * kTileBytes);
           for (int t = 0; t < 4; ++t)
             if (a.ymask >> t & 1)
-              for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][t][x], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
+              for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.y[st][x][t], &maps.y[t], &s.y_full[st], 64 * x, j * TILE, h, b);
           prefetch_y(n, j);
           if (j == jx && it + (int)gridDim.x < items && !(ok = load_x(it + gridDim.x, n + 1))) break;
         }
@@ -312,7 +314,8 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       // Pairs of products that share their A operand and whose B tiles / accumulators are adjacent are issued as
       // one instruction of twice the width: fewer instructions for the single issuing thread, and N = 128
       // instructions run at the full tensor rate where N = 64 ones reach about two thirds of it.
-      constexpr bool kMerge = (kBoxes == 1) && (2 * TILE <= 256) && (2 * D <= 256);
+      constexpr bool kMergeS = 2 * TILE <= 256;                   // score products: [S | Sd], [A | C]
+      constexpr bool kMerge = (kBoxes == 1) && (2 * D <= 256);    // output products: [dX1 | dX0], [dVd | dV]
       constexpr uint32_t idesc_s2 = make_idesc(kRows, 2 * TILE, kBf16, false, false);
       constexpr uint32_t idesc_o2 = make_idesc(kRows, 2 * D, kBf16, false, true);
       // the X2 Y3^T term of C carries G Vd^T for the query owner but V gO^T for the key owner, and vice versa
@@ -328,7 +331,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         return xlo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kXTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
       };
       auto yd = [&](uint32_t ylo, int t, int kk) {
-        return ylo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kYTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
+        return ylo + (uint32_t)((((kk >> 2) * 4 + t) * kYTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
       };
       // one accumulator at a time, 16 channels per instruction.  g = tile counter (stage / parity), xb = X buffer,
       // last = this is the item's last tile (its X tiles are released once no later score MMA needs them)
@@ -337,7 +340,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         if (!mbar_wait(&s.y_full[st], (g / kStages) & 1)) return false;
         tc_fence_after();
         const uint32_t xlo = xbase(xb), ylo = ybase(st);
-        if (kMerge && has_t) {
+        if (kMergeS && has_t) {
           // [S | Sd] = X0 [Y0 ; Y1]^T in one N = 2 TILE instruction per step, then Sd += X1 Y0^T
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, xd(xlo, 0, kk), yd(ylo, 0, kk), idesc_s2, kk > 0);
@@ -364,7 +367,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         const int st = g % kStages;  // already resident: scores1 waited for it
         const uint32_t xlo = xbase(xb), ylo = ybase(st);
         bool c_started = false;
-        if (kMerge && has_t && term23) {
+        if (kMergeS && has_t && term23) {
           // [A | C] = X2 [Y2 ; Y3]^T in one N = 2 TILE instruction per step
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColA, xd(xlo, 2, kk), yd(ylo, 2, kk), idesc_s2, kk > 0);
@@ -388,9 +391,11 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         if (last) tc_commit(&s.x_empty[xb]);
         JVP_TRACE(6);
       };
-      constexpr uint32_t lbo = TILE * 128;  // bytes between 64-channel column blocks of a Y tile
+      // Y tiles as MN-major B operands of the output products: consecutive 64-channel blocks are the two boxes of
+      // one tensor (d = 128: four tiles apart) or, for the merged d = 64 products, two adjacent tensors
+      constexpr uint32_t lbo = (kBoxes == 1 ? 1 : 4) * TILE * 128;
       auto yb = [&](uint32_t ylo, int t, int kk) {
-        return ylo + (uint32_t)((t * kBoxes * kYTile + kk * 2048) >> 4) + desc_lo_mn_major(lbo);
+        return ylo + (uint32_t)((t * kYTile + kk * 2048) >> 4) + desc_lo_mn_major(lbo);
       };
       // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the start
       // of its own column range (see the score-algebra warps)
