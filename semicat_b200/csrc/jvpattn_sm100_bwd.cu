@@ -57,7 +57,7 @@ struct BwdSmem {
   // flight holds a scoreboard slot that the tensor-memory reads of the score algebra also wait on, which exposed
   // the memory latency once per item even with nothing depending on the load.
   alignas(16) float xstat[kXBuf][4][kRows];
-  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done;
+  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done, vdone;
   uint32_t tmem_base;
 };
 
@@ -177,6 +177,9 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   constexpr bool kBf16 = IsBf16<T>::value;
   constexpr uint32_t kTileBytes = TILE * D * 2;
   constexpr int CH = TILE / 2;  // score columns per compute thread and tile
+  // d = 64 key owner: dV / dVd are final one group before dK / dKd (their last products are issued ahead of the last
+  // tile's second half), so they are staged for the output stores while the tensor core finishes dK / dKd
+  constexpr bool kEarlyV = kKV && kDoK && kDoV && kBoxes == 1;
 
   constexpr int kXBuf = Smem::kXBuf;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,6 +211,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     mbar_init(&s.c1_done, kComputeThreads);
     mbar_init(&s.c2_done, kComputeThreads);
     mbar_init(&s.done, 1);
+    mbar_init(&s.vdone, 1);
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -468,6 +472,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
             }
           }
         }
+        if (kEarlyV && j == ntiles - 1) tc_commit(&s.vdone);  // dV / dVd of this item are final
         if (has_next) {
           if (j2 == 0 && !mbar_wait(&s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
             atomicExch(a.status, 202u);
@@ -672,12 +677,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       JVP_TRACE(13);
     }
     // ---- epilogue of the item: accumulators -> 16-bit outputs, each thread half of the channels of its row
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, n & 1))) {
-      atomicExch(a.status, 206u);
-      ok = false;
-    }
-    JVP_TRACE(14);
-    tc_fence_after();
     {
       const int xr = x0 + row;
       const bool live = xr < a.Lx;
@@ -719,13 +718,30 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, half * 4 + i)) = v;
         }
       };
+      if (kEarlyV) {
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.vdone, n & 1))) {
+          atomicExch(a.status, 214u);
+          ok = false;
+        }
+        tc_fence_after();
+        if (ok) {
+          stage_acc(kColV, 2);
+          if (has_t) stage_acc(kColVd, 3);
+        }
+      }
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, n & 1))) {
+        atomicExch(a.status, 206u);
+        ok = false;
+      }
+      JVP_TRACE(14);
+      tc_fence_after();
       if (kBoxes == 1) {
         const bool w0 = kDoK, w1 = kDoK && has_t, w2 = kDoV, w3 = kDoV && has_t;
         if (ok) {
           if (w0) stage_acc(kColK, 0);
           if (w1) stage_acc(kColKd, 1);
-          if (w2) stage_acc(kColV, 2);
-          if (w3) stage_acc(kColVd, 3);
+          if (w2 && !kEarlyV) stage_acc(kColV, 2);
+          if (w3 && !kEarlyV) stage_acc(kColVd, 3);
           fence_proxy_async();
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");
