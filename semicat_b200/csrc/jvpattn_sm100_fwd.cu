@@ -69,6 +69,24 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     mbar_init(&s.p_full, 128);
     mbar_init(&s.o_done, 1);
     fence_barrier_init();
+    // The barriers this thread just initialised are all the first requests need: the query rows and the first
+    // key tiles are on their way while the other warps allocate tensor memory and meet at the barrier below.
+    prefetch_tensormap(&maps.q);
+    prefetch_tensormap(&maps.k);
+    mbar_expect_tx(&s.q_full, 2 * kBM * D * 2);
+    for (int x = 0; x < kBoxes; ++x) {
+      tma_load_4d(s.q[x], &maps.q, &s.q_full, 64 * x, q0, h, b);
+      tma_load_4d(s.tq[x], &maps.tq, &s.q_full, 64 * x, q0, h, b);
+    }
+    for (int j = 0; j < ntiles && j < kStages; ++j) {
+      mbar_expect_tx(&s.kv_full[j], 4 * kBN * D * 2);
+      for (int x = 0; x < kBoxes; ++x) {
+        tma_load_4d(s.kv[j][0][x], &maps.k, &s.kv_full[j], 64 * x, j * kBN, h, b);
+        tma_load_4d(s.kv[j][1][x], &maps.tk, &s.kv_full[j], 64 * x, j * kBN, h, b);
+        tma_load_4d(s.kv[j][2][x], &maps.v, &s.kv_full[j], 64 * x, j * kBN, h, b);
+        tma_load_4d(s.kv[j][3][x], &maps.tv, &s.kv_full[j], 64 * x, j * kBN, h, b);
+      }
+    }
   }
   if (warp == 1) {
     tmem_alloc(&s.tmem_base, kTmemCols);
@@ -82,14 +100,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      prefetch_tensormap(&maps.q);
-      prefetch_tensormap(&maps.k);
-      mbar_expect_tx(&s.q_full, 2 * kBM * D * 2);
-      for (int x = 0; x < kBoxes; ++x) {
-        tma_load_4d(s.q[x], &maps.q, &s.q_full, 64 * x, q0, h, b);
-        tma_load_4d(s.tq[x], &maps.tq, &s.q_full, 64 * x, q0, h, b);
-      }
-      for (int j = 0; j < ntiles; ++j) {
+      for (int j = kStages; j < ntiles; ++j) {  // the first kStages tiles were requested before the set-up barrier
         const int st = j % kStages;
         if (!mbar_wait(&s.kv_empty[st], ((j / kStages) & 1) ^ 1)) {
           atomicExch(a.status, 101u);
