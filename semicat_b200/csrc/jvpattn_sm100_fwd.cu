@@ -328,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         tma_store_4d(&maps.to, s.tq[x], 64 * x, q0, h, b);
       }
       tma_store_commit();
-      tma_store_wait_all();
+      tma_store_wait_read();  // the tiles must stay until the stores have read them; the writes finish on their own
     }
   }
 
