@@ -112,6 +112,7 @@ struct BwdKernelArgs {
 template <int D, typename T>
 __global__ void __launch_bounds__(256) row_dots_kernel(BwdArgs a, float *delta, float *dsum) {
   constexpr int kTpr = D / 8;
+  ptx::griddep_launch_dependents();  // the query-owner launch may set up while this kernel drains
   const int64_t nrows = (int64_t)a.B * a.H * a.Lq;
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t r = gid / kTpr;
@@ -222,13 +223,15 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s.tmem_base;
-  // The key-owner launches read nothing that the query-owner launch writes, so they need not wait for it: the
-  // query owner (launched normally, i.e. after the row dots and everything earlier in the stream have completed)
-  // releases its dependents at once, and the key-owner CTAs, launched with the programmatic-serialization
-  // attribute, move onto SMs as the query-owner CTAs leave them.  That hides their launch and first loads and
-  // fills the tail in which only some SMs still hold a query-owner item.
-  if (!kKV) griddep_wait();
-  griddep_launch_dependents();
+  // Launch overlap (programmatic dependent launch).  The row-dot kernel is launched normally, so everything earlier
+  // in the stream has completed when it runs, and it releases its dependents at once.  The query owner, launched
+  // with the programmatic-serialization attribute, sets up and requests its first row tiles while the row-dot
+  // kernel drains; only its producer thread reads what that kernel wrote (delta, dsum), so that thread alone
+  // waits for it, and it releases the key-owner launches right after.  Those read nothing the query owner writes:
+  // their CTAs move onto SMs as query-owner CTAs leave, which hides their start-up and fills the tail in which
+  // only some SMs still hold a query-owner item.  A key-owner CTA can only exist after every query-owner producer
+  // has passed its wait, hence after the row dots are complete.
+  if (kKV) griddep_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -251,11 +254,13 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           if (a.xmask >> t & 1)
             for (int x = 0; x < kBoxes; ++x) tma_load_4d(s.x[xb][t][x], &maps.x[t], &s.x_full[xb], 64 * x, x0, h, b);
         if (!kKV) {
+          if (n_ == 0) griddep_wait();  // delta / dsum are the row-dot kernel's output
           const size_t si = ((size_t)b * a.H + h) * a.stat_len + x0;  // stat_len is a multiple of 128: always in bounds
           bulk_load_1d(s.xstat[xb][0], a.lse + si, kRows * 4, &s.x_full[xb]);
           if (has_t) bulk_load_1d(s.xstat[xb][1], a.mu + si, kRows * 4, &s.x_full[xb]);
           bulk_load_1d(s.xstat[xb][2], a.delta + si, kRows * 4, &s.x_full[xb]);
           bulk_load_1d(s.xstat[xb][3], a.dsum + si, kRows * 4, &s.x_full[xb]);
+          if (n_ == 0) griddep_launch_dependents();
         }
         if (kXBuf == 1 && it_ + (int)gridDim.x < items) {  // single X buffer: at least bring the next item's rows into L2
           decode(it_ + gridDim.x, b, h, x0);
@@ -823,8 +828,7 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
   dim3 grid((unsigned)std::min<int64_t>(items, sm_count()));  // persistent: one CTA per SM walks the items
   {
     LaunchScope scope(kKV ? kIdBwdKeyTc : kIdBwdQueryTc, stream);
-    if (kKV) e = launch_overlapped(kernel, grid, dim3(kThreads), smem, stream, maps, ka);
-    else kernel<<<grid, kThreads, smem, stream>>>(maps, ka);
+    e = launch_overlapped(kernel, grid, dim3(kThreads), smem, stream, maps, ka);
   }
   return e != cudaSuccess ? e : cudaGetLastError();
 }
