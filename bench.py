@@ -41,8 +41,8 @@ WORKLOADS = {
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload
 # (profiles/config2_launch_list_and_counters.md); None where no capture exists
-NCU_TRAFFIC = {"config2": {"sm100_bwd_kernel<key owner>": 118.7e6, "sm100_bwd_kernel<query owner>": 108.6e6,
-                           "sm100_fwd_kernel": 80.8e6}}
+NCU_TRAFFIC = {"config2": {"sm100_bwd_kernel<key owner>": 116.8e6, "sm100_bwd_kernel<query owner>": 110.9e6,
+                           "sm100_fwd_kernel": 80.3e6}}
 
 
 def flops_per_step(B, H, L, D):
