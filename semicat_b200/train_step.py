@@ -181,7 +181,10 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
         xt = interpolate(x0[split:], x1[split:], t.view(-1, 1, 1))
         with ac():
             pred = net(xt, t, t)
-        vf_loss = F.cross_entropy(pred.float().transpose(-1, 1), x1[split:], label_smoothing=label_smoothing)
+        # Same value as the reference's F.cross_entropy(pred.transpose(-1, 1), x1) (semicat.py:107-111): mean over all
+        # tokens.  With the classes innermost the log-softmax over the 30522-entry vocabulary runs as a row softmax;
+        # in the transposed (B, V, L) layout it is a strided "spatial" softmax that took a third of the whole step.
+        vf_loss = F.cross_entropy(pred.float().reshape(-1, pred.shape[-1]), x1[split:].reshape(-1), label_smoothing=label_smoothing)
     if split == 0:
         return vf_loss, None
     # self-distillation ("lag") step on the head of the batch: d/dt of the flow map by forward-mode AD
