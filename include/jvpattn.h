@@ -103,6 +103,18 @@ int jvpattn_bwd(const jvpattn_problem *p,
                 const jvpattn_tensor *dtq, const jvpattn_tensor *dtk, const jvpattn_tensor *dtv,
                 void *workspace, size_t workspace_bytes, void *stream);
 
+/* Caller-side helper (no counterpart in the reference's kernel wrappers; it replaces the pointwise chain in front
+ * of them: the fp32 rotary embedding of q and k, semicat/net/duo.py:52-53, and the cast to bf16 in safe_sdpa_jvp,
+ * semicat/jvp_utils/functional.py:318-321).  Rotates the two halves of the last axis of a strided (B, S, H, D)
+ * view `x` (element strides sb, ss, sh; last stride 1) by the angles in `cos`, `sin` (fp32, (S, D/2) contiguous) and
+ * writes a contiguous (B, S, H, D) tensor `y` of type `out_dtype`; `transpose` != 0 applies the transposed map (the
+ * VJP).  fp32 products and sums are rounded separately, so the result is the fp32 formula rounded once.
+ * dtype codes: JVPATTN_BF16, JVPATTN_FP16, JVPATTN_FP32.  D must be a multiple of 16. */
+#define JVPATTN_FP32 2
+int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
+                        const float *cos, const float *sin, int batch, int len, int heads, int head_dim, int transpose,
+                        void *stream);
+
 /* Same backward for callers that have no way to allocate device memory (no counterpart in the reference,
  * whose wrappers allocate freely through torch).  Takes no workspace: the scratch lives in a fixed
  * 2 MiB array inside the library image, present on every GPU that loads the library until the process
@@ -132,7 +144,7 @@ uint64_t jvpattn_launch_count(void);
  * triton.testing.do_bench around whole calls, ryu_triton.py:958-1007).  Between _begin and _end every
  * launch is bracketed by CUDA events on its stream; _end synchronises the device and returns, per kernel
  * id in [0, JVPATTN_NUM_KERNELS), the summed device time in milliseconds and the launch count. */
-#define JVPATTN_NUM_KERNELS 7
+#define JVPATTN_NUM_KERNELS 8
 int jvpattn_profile_begin(void);
 int jvpattn_profile_end(double *total_ms, uint64_t *launches);
 const char *jvpattn_kernel_name(int id);

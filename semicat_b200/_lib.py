@@ -16,7 +16,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG_DIR, "csrc")
 LIB_PATH = os.path.join(_PKG_DIR, "libjvpattn.so")
 SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu",
-           "sm100_tensormap.cu"]
+           "sm100_tensormap.cu", "rotary.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
@@ -29,10 +29,10 @@ EXPORTS = (
     "jvpattn_fwd", "jvpattn_bwd", "jvpattn_bwd_workspace_bytes", "jvpattn_selected_kernels",
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
-    "jvpattn_bwd_static",
+    "jvpattn_bwd_static", "jvpattn_rotary_cast",
 )
 STATIC_SCRATCH_ROWS = 262144
-NUM_KERNELS = 7
+NUM_KERNELS = 8
 
 
 class Tensor4(ctypes.Structure):
@@ -111,6 +111,9 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_bwd.restype = ctypes.c_int
         lib.jvpattn_bwd_static.argtypes = [P] + [T] * 10 + [F, F] + [T] * 6 + [ctypes.c_void_p]
         lib.jvpattn_bwd_static.restype = ctypes.c_int
+        lib.jvpattn_rotary_cast.argtypes = ([ctypes.c_void_p] + [ctypes.c_int64] * 3 + [ctypes.c_int, ctypes.c_void_p, ctypes.c_int,
+                                            ctypes.c_void_p, ctypes.c_void_p] + [ctypes.c_int] * 5 + [ctypes.c_void_p])
+        lib.jvpattn_rotary_cast.restype = ctypes.c_int
         lib.jvpattn_bwd_workspace_bytes.argtypes = [P]
         lib.jvpattn_bwd_workspace_bytes.restype = ctypes.c_size_t
         lib.jvpattn_selected_kernels.argtypes = [P, ctypes.c_int]

@@ -203,6 +203,19 @@ extern "C" {
 
 int jvpattn_abi_version(void) { return JVPATTN_ABI_VERSION; }
 
+int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
+                        const float *cosv, const float *sinv, int batch, int len, int heads, int head_dim, int transpose,
+                        void *stream) {
+  if (batch < 0 || len < 0 || heads < 0 || head_dim < 16 || head_dim % 16 != 0) return JVPATTN_EINVAL;
+  if (in_dtype < 0 || in_dtype > JVPATTN_FP32 || out_dtype < 0 || out_dtype > JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * len * heads == 0) return JVPATTN_OK;
+  if (!x || !y || !cosv || !sinv) return JVPATTN_EINVAL;
+  return note_cuda(rotary_cast(x, sb, ss, sh, in_dtype, y, out_dtype, cosv, sinv, batch, len, heads, head_dim, transpose,
+                               static_cast<cudaStream_t>(stream)));
+}
+
 uint64_t jvpattn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char *jvpattn_last_cuda_error(void) { return t_cuda_error; }
@@ -264,6 +277,7 @@ const char *jvpattn_kernel_name(int id) {
     case kIdFwdSimt: return "simt_fwd_kernel";
     case kIdBwdQuerySimt: return "simt_bwd_q_kernel";
     case kIdBwdKeySimt: return "simt_bwd_kv_kernel";
+    case kIdRotary: return "rotary_cast_kernel";
     default: return "?";
   }
 }

@@ -51,10 +51,13 @@ bool sm100_bwd_supported(const BwdArgs &a);
 cudaError_t sm100_fwd(const FwdArgs &a, cudaStream_t stream);
 cudaError_t sm100_bwd(const BwdArgs &a, cudaStream_t stream);
 size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_len);
+// rotary.cu: rotation by fixed angles fused with the cast (dtype codes 0 bf16, 1 fp16, 2 fp32)
+cudaError_t rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
+                        const float *cosv, const float *sinv, int B, int S, int H, int D, int transpose, cudaStream_t stream);
 
 // Kernel identifiers used by the launch counter and the optional per-kernel event timing.
 enum KernelId {
-  kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kNumKernelIds
+  kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kIdRotary, kNumKernelIds
 };
 
 // Brackets one kernel launch: counts it and, while profiling is on, records a CUDA event before and

@@ -1,0 +1,101 @@
+// Rotary position embedding fused with the cast to the attention kernels' 16-bit input type.
+//
+// The denoiser rotates q and k in fp32 (semicat/net/duo.py:52-53, non-interleaved halves) and safe_sdpa_jvp then
+// casts them to bf16 (semicat/jvp_utils/functional.py:318-321); under forward-mode AD every one of those
+// pointwise steps runs once for the primal and once for the tangent.  This kernel does rotation and rounding in
+// one pass over a strided (B, S, H, D) view and writes a contiguous (B, S, H, D) tensor:
+//   y[..., :D/2] = x1 * cos - x2 * sin        y[..., D/2:] = x1 * sin + x2 * cos         (transpose = 0)
+//   y[..., :D/2] = x1 * cos + x2 * sin        y[..., D/2:] = x2 * cos - x1 * sin         (transpose = 1: the VJP)
+// Products and sums are separate fp32 roundings (no fused multiply-add), so the result equals the fp32 PyTorch
+// formula rounded once to the output type, bit for bit.  The map is linear: the same kernel serves the tangent.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "jvpattn_common.cuh"
+
+namespace jvpattn {
+namespace {
+
+template <typename T> struct Io;
+template <> struct Io<float> {
+  static __device__ __forceinline__ float load(const float *p) { return *p; }
+  static __device__ __forceinline__ void store(float *p, float v) { *p = v; }
+};
+template <> struct Io<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+};
+template <> struct Io<__half> {
+  static __device__ __forceinline__ float load(const __half *p) { return __half2float(*p); }
+  static __device__ __forceinline__ void store(__half *p, float v) { *p = __float2half_rn(v); }
+};
+
+// One thread = 8 consecutive channels of the first half of one (b, s, h) row and the matching 8 of the second half.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) rotary_cast_kernel(const TI *x, int64_t sb, int64_t ss, int64_t sh, TO *y,
+                                                          const float *cosv, const float *sinv, int B, int S, int H, int D,
+                                                          int transpose) {
+  const int half = D / 2, per_row = half / 8;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t rows = (int64_t)B * S * H;
+  const int64_t r = gid / per_row;
+  if (r >= rows) return;
+  const int c0 = (int)(gid % per_row) * 8;
+  const int h = (int)(r % H);
+  const int s = (int)((r / H) % S);
+  const int b = (int)(r / ((int64_t)H * S));
+  const TI *xr = x + b * sb + s * ss + h * sh;
+  TO *yr = y + r * D;
+  const float *cr = cosv + (int64_t)s * half + c0, *sr = sinv + (int64_t)s * half + c0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x1 = Io<TI>::load(xr + c0 + i), x2 = Io<TI>::load(xr + half + c0 + i);
+    const float c = cr[i], sn = sr[i];
+    float y1, y2;
+    if (transpose) {
+      y1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+      y2 = __fsub_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+    } else {
+      y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
+      y2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+    }
+    Io<TO>::store(yr + c0 + i, y1);
+    Io<TO>::store(yr + half + c0 + i, y2);
+  }
+}
+
+template <typename TI, typename TO>
+cudaError_t launch(const void *x, int64_t sb, int64_t ss, int64_t sh, void *y, const float *cosv, const float *sinv, int B,
+                   int S, int H, int D, int transpose, cudaStream_t stream) {
+  const int64_t threads = (int64_t)B * S * H * (D / 16);
+  if (threads == 0) return cudaSuccess;
+  {
+    LaunchScope scope(kIdRotary, stream);
+    rotary_cast_kernel<TI, TO><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+        static_cast<const TI *>(x), sb, ss, sh, static_cast<TO *>(y), cosv, sinv, B, S, H, D, transpose);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+// dtype codes: 0 bf16, 1 fp16, 2 fp32 (include/jvpattn.h)
+cudaError_t rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
+                        const float *cosv, const float *sinv, int B, int S, int H, int D, int transpose, cudaStream_t stream) {
+#define JVP_ROT(TI, TO) return launch<TI, TO>(x, sb, ss, sh, y, cosv, sinv, B, S, H, D, transpose, stream)
+  switch (in_dtype * 3 + out_dtype) {
+    case 0: JVP_ROT(__nv_bfloat16, __nv_bfloat16);
+    case 1: JVP_ROT(__nv_bfloat16, __half);
+    case 2: JVP_ROT(__nv_bfloat16, float);
+    case 3: JVP_ROT(__half, __nv_bfloat16);
+    case 4: JVP_ROT(__half, __half);
+    case 5: JVP_ROT(__half, float);
+    case 6: JVP_ROT(float, __nv_bfloat16);
+    case 7: JVP_ROT(float, __half);
+    case 8: JVP_ROT(float, float);
+    default: return cudaErrorInvalidValue;
+  }
+#undef JVP_ROT
+}
+
+}  // namespace jvpattn

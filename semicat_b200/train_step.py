@@ -24,6 +24,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .functional import safe_sdpa_jvp
+from .rotary import apply_rotary_cast
 
 
 def _rotate(x, cos, sin):
@@ -65,7 +66,13 @@ class Block(nn.Module):
         sh1, sc1, g1, sh2, sc2, g2 = self.ada(c)[:, None].chunk(6, dim=2)
         h = self.norm1(x) * (1.0 + sc1) + sh1
         q, k, v = self.attn_qkv(h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
-        q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
+        if x.is_cuda and attention != "math":
+            # one kernel per tensor (and per tangent) instead of the fp32 pointwise chain plus the casts to bf16
+            rot_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
+            q, k = apply_rotary_cast(q, cos, sin, rot_dtype), apply_rotary_cast(k, cos, sin, rot_dtype)
+            v = v.to(rot_dtype)
+        else:
+            q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
         if attention == "jvp":
             a = safe_sdpa_jvp(q, k, v)
         elif attention == "math":  # plain formula: supports forward-mode AD anywhere (used by the CPU tests)

@@ -1,0 +1,75 @@
+"""GPU parity of the fused rotary + cast helper (``jvpattn_rotary_cast`` through ``semicat_b200.rotary``).
+
+Oracle: the reference's non-interleaved rotary formula (flash_attn ``apply_rotary_emb_torch`` as called at
+semicat/net/duo.py:52-53) evaluated with fp32 PyTorch ops and rounded once to the output type.  The kernel
+rounds every product and sum separately, so forward values, tangents and VJPs must agree bit for bit."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from semicat_b200 import _lib
+    from semicat_b200.rotary import apply_rotary_cast
+
+
+def _tables(S, D, device):
+    ang = torch.arange(S, device=device)[:, None] * (1.0 / (10000 ** (torch.arange(0, D, 2, device=device) / D)))[None]
+    return ang.cos().float(), ang.sin().float()
+
+
+def _formula(x, cos, sin):
+    half = x.shape[-1] // 2
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    c, s = cos[None, :, None, :], sin[None, :, None, :]
+    return torch.cat((x1 * c - x2 * s, x1 * s + x2 * c), dim=-1)
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(2, 128, 12, 64), (1, 33, 3, 128), (3, 7, 1, 16)])
+def test_forward_is_the_fp32_formula_rounded_once(shape, in_dtype, out_dtype):
+    B, S, H, D = shape
+    g = torch.Generator(device="cuda").manual_seed(7)
+    # a strided view, as the qkv projection hands it over: (B, S, 3, H, D).unbind(2)
+    qkv = torch.randn(B, S, 3, H, D, device="cuda", generator=g).to(in_dtype)
+    x = qkv.unbind(2)[1]
+    cos, sin = _tables(S, D, "cuda")
+    before = _lib.launch_count()
+    y = apply_rotary_cast(x, cos, sin, out_dtype)
+    assert _lib.launch_count() == before + 1
+    assert y.dtype == out_dtype and y.is_contiguous() and y.shape == x.shape
+    assert torch.equal(y, _formula(x, cos, sin).to(out_dtype))
+
+
+def test_tangent_and_gradients_match_autograd_of_the_formula():
+    B, S, H, D = 2, 64, 4, 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(B, S, H, D, device="cuda", generator=g).bfloat16()
+    t = torch.randn(B, S, H, D, device="cuda", generator=g).bfloat16()
+    gy = torch.randn(B, S, H, D, device="cuda", generator=g)
+    gt = torch.randn(B, S, H, D, device="cuda", generator=g)
+    cos, sin = _tables(S, D, "cuda")
+
+    def run(fn):
+        xl, tl = x.clone().requires_grad_(True), t.clone().requires_grad_(True)
+        y, ty = torch.func.jvp(fn, (xl,), (tl,))
+        gx, gtl = torch.autograd.grad([y, ty], [xl, tl], [gy.to(y.dtype), gt.to(ty.dtype)])
+        return y, ty, gx, gtl
+
+    fused = run(lambda z: apply_rotary_cast(z, cos, sin, torch.float32))
+    plain = run(lambda z: _formula(z, cos, sin))
+    for name, a, b in zip(("y", "ty", "dx", "dt"), fused, plain):
+        assert a.dtype == b.dtype, name
+        assert torch.equal(a, b), f"{name}: max diff {(a.float() - b.float()).abs().max().item()}"
+
+
+def test_rejects_what_it_cannot_run():
+    cos, sin = _tables(8, 64, "cuda")
+    with pytest.raises(RuntimeError):
+        apply_rotary_cast(torch.zeros(1, 8, 1, 64), cos.cpu(), sin.cpu())
+    with pytest.raises(ValueError):
+        apply_rotary_cast(torch.zeros(1, 8, 1, 24, device="cuda"), cos, sin)
+    assert math.isfinite(float(apply_rotary_cast(torch.zeros(0, 8, 1, 64, device="cuda"), cos, sin).sum()))
