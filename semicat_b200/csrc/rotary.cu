@@ -30,8 +30,35 @@ template <> struct Io<__half> {
   static __device__ __forceinline__ void store(__half *p, float v) { *p = __float2half_rn(v); }
 };
 
+// 8 consecutive elements as fp32, by 16-byte accesses (pointers 16-byte aligned)
+template <typename T> struct Vec8 {
+  static __device__ __forceinline__ void load(const T *p, float (&f)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4 *>(p);
+    const T *e = reinterpret_cast<const T *>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = Io<T>::load(e + i);
+  }
+  static __device__ __forceinline__ void store(T *p, const float (&f)[8]) {
+    uint4 u;
+    T *e = reinterpret_cast<T *>(&u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) Io<T>::store(e + i, f[i]);
+    *reinterpret_cast<uint4 *>(p) = u;
+  }
+};
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float *p, float (&f)[8]) {
+    const float4 a = reinterpret_cast<const float4 *>(p)[0], b = reinterpret_cast<const float4 *>(p)[1];
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float *p, const float (&f)[8]) {
+    reinterpret_cast<float4 *>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+    reinterpret_cast<float4 *>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
 // One thread = 8 consecutive channels of the first half of one (b, s, h) row and the matching 8 of the second half.
-template <typename TI, typename TO>
+template <typename TI, typename TO, bool kVec>
 __global__ void __launch_bounds__(256) rotary_cast_kernel(const TI *x, int64_t sb, int64_t ss, int64_t sh, TO *y,
                                                           const float *cosv, const float *sinv, int B, int S, int H, int D,
                                                           int transpose) {
@@ -47,20 +74,40 @@ __global__ void __launch_bounds__(256) rotary_cast_kernel(const TI *x, int64_t s
   const TI *xr = x + b * sb + s * ss + h * sh;
   TO *yr = y + r * D;
   const float *cr = cosv + (int64_t)s * half + c0, *sr = sinv + (int64_t)s * half + c0;
+  float x1[8], x2[8], c[8], sn[8], y1[8], y2[8];
+  if (kVec) {
+    Vec8<TI>::load(xr + c0, x1);
+    Vec8<TI>::load(xr + half + c0, x2);
+    Vec8<float>::load(cr, c);
+    Vec8<float>::load(sr, sn);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      x1[i] = Io<TI>::load(xr + c0 + i);
+      x2[i] = Io<TI>::load(xr + half + c0 + i);
+      c[i] = cr[i];
+      sn[i] = sr[i];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    const float x1 = Io<TI>::load(xr + c0 + i), x2 = Io<TI>::load(xr + half + c0 + i);
-    const float c = cr[i], sn = sr[i];
-    float y1, y2;
     if (transpose) {
-      y1 = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
-      y2 = __fsub_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn));
+      y1[i] = __fadd_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i]));
+      y2[i] = __fsub_rn(__fmul_rn(x2[i], c[i]), __fmul_rn(x1[i], sn[i]));
     } else {
-      y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn));
-      y2 = __fadd_rn(__fmul_rn(x1, sn), __fmul_rn(x2, c));
+      y1[i] = __fsub_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i]));
+      y2[i] = __fadd_rn(__fmul_rn(x1[i], sn[i]), __fmul_rn(x2[i], c[i]));
     }
-    Io<TO>::store(yr + c0 + i, y1);
-    Io<TO>::store(yr + half + c0 + i, y2);
+  }
+  if (kVec) {
+    Vec8<TO>::store(yr + c0, y1);
+    Vec8<TO>::store(yr + half + c0, y2);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      Io<TO>::store(yr + c0 + i, y1[i]);
+      Io<TO>::store(yr + half + c0 + i, y2[i]);
+    }
   }
 }
 
@@ -69,10 +116,19 @@ cudaError_t launch(const void *x, int64_t sb, int64_t ss, int64_t sh, void *y, c
                    int S, int H, int D, int transpose, cudaStream_t stream) {
   const int64_t threads = (int64_t)B * S * H * (D / 16);
   if (threads == 0) return cudaSuccess;
+  // 16-byte accesses when every row of x, y and the tables starts on a 16-byte boundary
+  const bool vec = reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0 &&
+                   reinterpret_cast<uintptr_t>(cosv) % 16 == 0 && reinterpret_cast<uintptr_t>(sinv) % 16 == 0 &&
+                   sb % 8 == 0 && ss % 8 == 0 && sh % 8 == 0;
   {
     LaunchScope scope(kIdRotary, stream);
-    rotary_cast_kernel<TI, TO><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
-        static_cast<const TI *>(x), sb, ss, sh, static_cast<TO *>(y), cosv, sinv, B, S, H, D, transpose);
+    const unsigned grid = (unsigned)((threads + 255) / 256);
+    if (vec)
+      rotary_cast_kernel<TI, TO, true><<<grid, 256, 0, stream>>>(static_cast<const TI *>(x), sb, ss, sh, static_cast<TO *>(y),
+                                                                 cosv, sinv, B, S, H, D, transpose);
+    else
+      rotary_cast_kernel<TI, TO, false><<<grid, 256, 0, stream>>>(static_cast<const TI *>(x), sb, ss, sh, static_cast<TO *>(y),
+                                                                  cosv, sinv, B, S, H, D, transpose);
   }
   return cudaGetLastError();
 }

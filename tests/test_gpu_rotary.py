@@ -73,3 +73,12 @@ def test_rejects_what_it_cannot_run():
     with pytest.raises(ValueError):
         apply_rotary_cast(torch.zeros(1, 8, 1, 24, device="cuda"), cos, sin)
     assert math.isfinite(float(apply_rotary_cast(torch.zeros(0, 8, 1, 64, device="cuda"), cos, sin).sum()))
+
+
+def test_unaligned_views_take_the_scalar_path():
+    B, S, H, D = 2, 9, 3, 32
+    g = torch.Generator(device="cuda").manual_seed(11)
+    buf = torch.randn(B, S, H, D + 3, device="cuda", generator=g).bfloat16()
+    x = buf[..., 1:D + 1]  # row starts 2 bytes off a 16-byte boundary, row pitch not a multiple of 8 elements
+    cos, sin = _tables(S, D, "cuda")
+    assert torch.equal(apply_rotary_cast(x, cos, sin, torch.bfloat16), _formula(x, cos, sin).bfloat16())
