@@ -36,6 +36,29 @@ def _rotate(x, cos, sin):
     return torch.cat((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
 
 
+def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0):
+    """``lin(x * in_scale)`` with the vocabulary-sized dimension padded to a multiple of 8 elements.
+
+    30522 is not a multiple of 8, so the operand rows of the embedding and head GEMMs are only 4-byte aligned and
+    the BLAS library falls back to its pre-Hopper kernels for them (17 % of the step).  Zero columns / rows change
+    nothing in the products; ``in_scale`` is folded into the weight instead of a pass over the (B, L, V) input."""
+    w, b = lin.weight, lin.bias
+    if in_scale != 1.0:
+        w = w * in_scale
+    if not x.is_cuda:
+        return F.linear(x, w, b)
+    n_out, n_in = w.shape
+    pad_in, pad_out = (-n_in) % 8, (-n_out) % 8
+    if pad_in:
+        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
+        x, w = F.pad(x.to(dt), (0, pad_in)), F.pad(w.to(dt), (0, pad_in))
+    if pad_out:
+        w = F.pad(w, (0, 0, 0, pad_out))
+        b = F.pad(b, (0, pad_out)) if b is not None else None
+    y = F.linear(x, w, b)
+    return y[..., :n_out] if pad_out else y
+
+
 class TimeEmbed(nn.Module):
     def __init__(self, dim, n_freq=256, max_period=10000):
         super().__init__()
@@ -113,7 +136,7 @@ class NaiveEmbed(nn.Module):
         self.coeff = vocab ** 0.5
 
     def forward(self, x, t, cond):
-        return self.seq(x / self.coeff)
+        return _aligned_linear(x, self.seq, 1.0 / self.coeff)
 
 
 class DiT(nn.Module):
@@ -140,7 +163,7 @@ class DiT(nn.Module):
         for blk in self.blocks:
             h = blk(h, self.cos, self.sin, cond, attention)
         shift, scale = self.ada_out(cond)[:, None].chunk(2, dim=2)
-        return self.head(self.norm_out(h) * (1.0 + scale) + shift)
+        return _aligned_linear(self.norm_out(h) * (1.0 + scale) + shift, self.head)
 
 
 def randomise_zero_init(net: nn.Module, std=0.05, seed=0):
