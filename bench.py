@@ -39,10 +39,20 @@ WORKLOADS = {
     "L2048_d128_small": dict(B=2, H=16, L=2048, D=128, q_scale=1.0, t_scale=1.0),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload
-# (profiles/config2_launch_list_and_counters.md); None where no capture exists
-NCU_TRAFFIC = {"config2": {"sm100_bwd_kernel<key owner>": 116.8e6, "sm100_bwd_kernel<query owner>": 110.9e6,
-                           "sm100_fwd_kernel": 80.3e6}}
+# The same `config` object is printed by the GPU arm and by `--impl reference`, so that the two lines can be matched.
+TIMING_NOTE = ("GPU arm: rotating over >= 4 resident input/output sets (> 400 MB) so that no step finds its data in the "
+               "126 MB L2, one CUDA graph per set (eager launches where capture is unavailable; see launch_mode); "
+               "CPU arm: inputs drawn once outside the timed region")
+
+
+def ncu_traffic(workload, kernel):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel`, from the ncu capture recorded in
+    profiles/ncu_traffic.json (written when a capture is taken); None where no capture covers it."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            return json.load(f).get(workload, {}).get(kernel)
+    except Exception:
+        return None
 
 
 def flops_per_step(B, H, L, D):
@@ -279,10 +289,29 @@ TRAIN_CONFIGS = {
 }
 
 
-def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp", use_graph=True):
+def attention_jvp_flops(batch, heads, length, head_dim, layers, mode="lag"):
+    """Algorithmic FLOPs of the library's attention calls in one self-distillation step: forward 6 GEMM-units,
+    backward 13 with the cotangent of the tangent output alone (`lag`), 15 with both."""
+    units = 6 + (13 if mode == "lag" else 15)
+    return float(units) * 2.0 * batch * heads * length * length * head_dim * layers
+
+
+def count_step_flops(body, attn_flops):
+    """FLOPs of one eager training step: what torch.utils.flop_counter sees (matmuls and library attention of the
+    torch ops, primal and tangent passes, forward and backward) plus the algorithmic FLOPs of this library's own
+    attention kernels, which the counter cannot see."""
+    from torch.utils.flop_counter import FlopCounterMode
+    with FlopCounterMode(display=False) as fc:
+        body()
+    return float(fc.get_total_flops()) + attn_flops
+
+
+def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp", use_graph=True,
+              primal_attention="sdpa"):
     """Flow-map training steps of the DiT (semicat_b200/train_step.py) on uniform random tokens: global batch
     sharded over the ranks, forward-mode JVP through every attention layer for the first `sd_prop` of each
-    shard, AdamW, one flat gradient all-reduce per step.  Returns (ms per step, tokens per step, last loss)."""
+    shard, AdamW, one flat gradient all-reduce per step.  Every step copies its token ids from pinned host memory
+    and writes its loss back to the host.  Returns a dict (times in ms, max over ranks)."""
     import torch
     from semicat_b200 import ddp, train_step
     tc = TRAIN_CONFIGS[name]
@@ -292,17 +321,17 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True, capturable=True)
     lo, hi = ddp.shard_bounds(tc["global_batch"], rank, world)
     gen = torch.Generator().manual_seed(99 + rank)
+    # a ring of pinned token batches that the host never rewrites: the copy of step i cannot race with anything
     host_tokens = [torch.randint(0, tc["vocab"], (hi - lo, tc["length"]), generator=gen).pin_memory() for _ in range(4)]
     torch.cuda.manual_seed(7 + rank)  # per-rank noise from the default CUDA generator (graph-capturable)
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
-    tok_stage = torch.empty_like(host_tokens[0]).pin_memory()  # the host refills this buffer before every step
     x1 = torch.empty(hi - lo, tc["length"], dtype=torch.long, device=device)
 
     def body():
-        x1.copy_(tok_stage, non_blocking=True)
         noise = train_step.draw_noise(x1, tc["vocab"])
         flat.zero()
-        vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention)
+        vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention,
+                                       primal_attention=primal_attention)
         loss = train_step.total_loss(vf, sd)
         loss.backward()
         flat.all_reduce_mean()
@@ -312,20 +341,23 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     graph = None
 
     def step(i):
-        tok_stage.copy_(host_tokens[i % 4])
+        x1.copy_(host_tokens[i % 4], non_blocking=True)  # stream-ordered before the (graph of the) step
         if graph is not None:
             graph.replay()
         else:
             body()
 
-    for i in range(warmup):
+    x1.copy_(host_tokens[0])
+    n_sd = int(sd_prop * (hi - lo))
+    step_flops = count_step_flops(body, attention_jvp_flops(n_sd, 12, tc["length"], 64, 12) if attention == "jvp" else 0.0)
+    for i in range(max(warmup - 1, 2)):
         step(i)
     torch.cuda.synchronize()
     mode = "eager"
     if use_graph:
         # The step is launch-bound on the host (thousands of small kernels under forward-mode AD), so the whole
-        # step - H2D of the tokens, noise, forward/JVP, backward, gradient all-reduce, AdamW, D2H of the loss -
-        # is captured once into a CUDA graph and replayed.
+        # step - noise, forward/JVP, backward, gradient all-reduce, AdamW, D2H of the loss - is captured once into
+        # a CUDA graph and replayed; the H2D copy of the tokens is enqueued in front of every replay.
         try:
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
@@ -348,34 +380,79 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     with sampler:
-        start.record()
+        marks[0].record()
         for i in range(steps):
             step(i)
-        end.record()
-        end.synchronize()
+            marks[i + 1].record()
+        marks[-1].synchronize()
     if dist is not None:
         dist.barrier()
-    ms = start.elapsed_time(end) / steps
+    per_step = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+    ms = marks[0].elapsed_time(marks[-1]) / steps
+    med = statistics.median(per_step)
+    last_loss = float(loss_host)
+    # the gradient all-reduce alone (the only collective of the step), on the same flat buffer
+    ar = []
     if dist is not None:
-        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier()
+            a.record()
+            flat.all_reduce_mean()
+            b.record()
+            b.synchronize()
+            ar.append(a.elapsed_time(b))
+    ar_ms = statistics.median(ar[2:]) if ar else 0.0
+    if dist is not None:
+        t = torch.tensor([ms, med, ar_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+        ms, med, ar_ms = float(t[0]), float(t[1]), float(t[2])
+        f = torch.tensor([step_flops], device=device, dtype=torch.float64)
+        dist.all_reduce(f, op=dist.ReduceOp.SUM)
+        step_flops = float(f[0])
     peak_gb = torch.cuda.max_memory_allocated() / 1e9
     graph = None
+    nbytes = flat.nbytes()
     del net, opt, flat
     torch.cuda.empty_cache()
-    return ms, tc["global_batch"] * tc["length"], float(loss_host), peak_gb, mode
+    return {"ms_per_step": ms, "ms_per_step_median": med, "tokens_per_step": tc["global_batch"] * tc["length"],
+            "loss": last_loss, "peak_mem_gb": peak_gb, "launch": mode, "allreduce_ms": ar_ms, "allreduce_bytes": nbytes,
+            "flops_per_step": step_flops, "steps": steps, "warmup": max(warmup, 3), "primal_attention": primal_attention}
+
+
+def train_block(r, world, pk, label):
+    """The `train` object of the JSON line from run_train's result."""
+    tps = r["tokens_per_step"] / (r["ms_per_step"] * 1e-3)
+    tf = r["flops_per_step"] / (r["ms_per_step"] * 1e-3) / 1e12
+    return {"workload": label, "scaling": "strong", "ms_per_step": r["ms_per_step"], "ms_per_step_median": r["ms_per_step_median"],
+            "tokens_per_s": tps, "tokens_per_s_median": r["tokens_per_step"] / (r["ms_per_step_median"] * 1e-3),
+            "steps": r["steps"], "warmup": r["warmup"], "loss": r["loss"], "launch": r["launch"], "peak_mem_gb": r["peak_mem_gb"],
+            "primal_attention": r["primal_attention"],
+            "allreduce_ms": r["allreduce_ms"], "allreduce_bytes": r["allreduce_bytes"],
+            "flops_per_step": r["flops_per_step"], "flops_source": "torch.utils.flop_counter over one eager step + algorithmic "
+            "FLOPs of the library's attention calls", "tflops": tf, "frac_of_bf16_peak": tf / (world * pk["bf16_tflops"])}
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
-def cpu_path(cfg, repeats, threads=None):
-    """The CPU path of the reference (math attention under torch.func.jvp, differentiated by autograd),
-    restated in oracle/torch_cpu_path.py, timed on the host cores over the full workload in fp32."""
+def cpu_arm():
+    """The CPU implementation of the path that the CPU legs time: the reference's own
+    naive_multihead_attention_jvp (semicat/jvp_utils/ryu_triton.py:426-454) differentiated by autograd when the copy of
+    the reference package made by oracle/make_ref.py is present ("reference"), else its restatement in
+    oracle/torch_cpu_path.py ("port").  Returns (callable or None for the port, kind)."""
     from oracle import torch_cpu_path
-    best, used = torch_cpu_path.time_fwd_bwd(cfg["B"], cfg["H"], cfg["L"], cfg["D"], repeats=repeats, threads=threads)
-    return best, used
+    fn = torch_cpu_path.reference_attention_jvp()
+    return fn, ("reference" if fn is not None else "port")
+
+
+def cpu_path(cfg, repeats, threads=None):
+    """Best-of-`repeats` seconds of one fwd+bwd of the CPU arm over the full workload in fp32, on all host threads."""
+    from oracle import torch_cpu_path
+    fn, kind = cpu_arm()
+    best, used = torch_cpu_path.time_fwd_bwd(cfg["B"], cfg["H"], cfg["L"], cfg["D"], repeats=repeats, threads=threads,
+                                             attention=fn)
+    return best, used, kind
 
 
 def _claim_stdout():
@@ -405,6 +482,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS) + ["sweep5"])
     ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
+    ap.add_argument("--primal-attention", default="sdpa", choices=["sdpa", "lib"],
+                    help="attention of the passes without tangents in the training workloads: torch SDPA or this library")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
@@ -421,7 +500,7 @@ def main():
     flops = flops_per_step(B, H, L, D)
     config = {"workload": f"{args.workload}: JVP attention fwd+bwd, bf16, non-causal, B{B} H{H} L{L} d{D}, "
                           "both cotangents, (B,S,H,D) memory layout",
-              "flop_model": "42*B*H*L^2*d per step (6 fwd + 15 bwd GEMM-units)"}
+              "flop_model": "42*B*H*L^2*d per step (6 fwd + 15 bwd GEMM-units)", "l2": TIMING_NOTE}
 
     if args.impl == "reference":
         if rank != 0:
@@ -430,20 +509,27 @@ def main():
         cores = os.cpu_count() or 1
         torch.set_num_threads(cores)
         from oracle import torch_cpu_path
-        for _ in range(min(args.warmup, 2)):
-            torch_cpu_path.time_fwd_bwd(B, H, L, D, repeats=1, threads=cores)
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            torch_cpu_path.time_fwd_bwd(B, H, L, D, repeats=1, threads=cores)
-        ms = (time.perf_counter() - t0) * 1e3 / max(args.steps, 1)
+        fn, kind = cpu_arm()
+        inputs = torch_cpu_path.make_inputs(B, H, L, D, torch.float32, seed=0)  # drawn once, outside the timed region
+        for _ in range(max(min(args.warmup, 3), 1)):
+            torch_cpu_path.fwd_bwd(inputs, fn)
+        times = []
+        for _ in range(max(args.steps, 1)):
+            t0 = time.perf_counter()
+            torch_cpu_path.fwd_bwd(inputs, fn)
+            times.append((time.perf_counter() - t0) * 1e3)
+        ms = sum(times) / len(times)
         val = flops / (ms * 1e-3) / 1e12
-        config["l2"] = "n/a (host)"
+        what = ("the reference's naive_multihead_attention_jvp + torch.autograd.grad" if kind == "reference"
+                else "restatement of the reference's naive_multihead_attention_jvp + torch.autograd.grad")
         print(json.dumps({
-            "impl": "reference", "metric": "jvp_attn_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": 0,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "impl": "reference", "metric": "jvp_attn_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "ms_per_step_median": statistics.median(times),
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
-            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                             "sample": "the full workload per step, fp32, torch math attention under torch.func.jvp + autograd"},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": kind,
+                             "sample": f"the full workload per step (one batch of B{B} H{H} L{L} d{D}), fp32, {what}; "
+                                       "rank 0 only"},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0,
         }))
@@ -470,11 +556,10 @@ def main():
         host_sets.append(host_inputs(cfg, seed=1000 * rank + len(sets)))
         sets.append(DeviceSet(host_sets[-1], device))
         resident_mb = sum(s.nbytes() for s in sets) / 1e6
-    config["l2"] = f"rotating over {len(sets)} resident input/output sets ({resident_mb:.0f} MB) > 126 MB L2"
+    resident_note = f"{len(sets)} resident input/output sets, {resident_mb:.0f} MB"
 
     sampler = ClockSampler(local_rank)
     ms, launched, mode = run_device(cfg, sets, args.steps, args.warmup, dist, sampler, use_graph=not args.profile_mode)
-    config["launch"] = mode
     e2e_steps = max(3, min(args.steps, 20))
     if args.profile_mode:
         args.no_extras = True
@@ -495,7 +580,7 @@ def main():
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps, "api": "sdpa_jvp under torch.func.jvp + torch.autograd.grad, pinned host buffers, two steps in flight on two streams"},
-        "gpu_launches": int(launched),
+        "gpu_launches": int(launched), "launch_mode": mode, "resident": resident_note,
     }
 
     if rank == 0:
@@ -526,7 +611,7 @@ def main():
         if bound == "hbm":
             line["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gb_s"], "peak": pk["hbm_gbs"],
                                 "unit": "GB/s", "frac": top["gb_s"] / pk["hbm_gbs"],
-                                "traffic": NCU_TRAFFIC.get(args.workload, {}).get(top["kernel"]),
+                                "traffic": ncu_traffic(args.workload, top["kernel"]),
                                 "peak_source": pk["source"]}
         else:
             line["roofline"] = {"bound": "tensor", "kernel": top["kernel"], "achieved": top["executed_tflops"],
@@ -550,8 +635,8 @@ def main():
                                      "tflops": tf, "frac_of_bf16_peak": tf / pk["bf16_tflops"],
                                      "kernel_ms": {k_: v_[0] / v_[1] for k_, v_ in bprof.items()}}
             del bsets
-            cpu_s, cores = cpu_path(cfg, repeats=3)
-            line["cpu_baseline"] = {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            cpu_s, cores, cpu_kind = cpu_path(cfg, repeats=3)
+            line["cpu_baseline"] = {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": cpu_kind,
                                     "sample": "the full config-2 workload, fp32, best of 3 "
                                               f"({cpu_s * 1e3:.0f} ms per fwd+bwd)"}
     if not args.no_extras:
@@ -559,11 +644,10 @@ def main():
         try:
             sets = host_sets = None  # release the attention buffers before the model is built
             torch.cuda.empty_cache()
-            tms, tokens, tloss, peak_gb, tmode = run_train("dit_lm1b", 3, 3, device, rank, world, dist, sampler, sd_prop=0.25)
-            line["train"] = {"workload": "DiT 12x768, 12 heads, vocab 30522, seq 128, global batch 512, sd_prop 0.25 (lag), "
-                                         "bf16 autocast, AdamW, uniform random tokens", "scaling": "strong",
-                             "ms_per_step": tms, "tokens_per_s": tokens / (tms * 1e-3), "steps": 3, "loss": tloss, "launch": tmode,
-                             "peak_mem_gb": peak_gb}
+            tr = run_train("dit_lm1b", max(args.steps, 20) if args.steps >= 20 else args.steps, max(args.warmup, 5) if args.steps >= 20 else max(args.warmup, 3),
+                           device, rank, world, dist, ClockSampler(local_rank), sd_prop=0.25)
+            line["train"] = train_block(tr, world, peaks(), "DiT 12x768, 12 heads, vocab 30522, seq 128, global batch 512, "
+                                        "sd_prop 0.25 (lag), bf16 autocast, AdamW, uniform random tokens")
         except Exception as e:  # the attention line above stands on its own
             line["train"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     if rank == 0:
@@ -614,8 +698,9 @@ def main_train(args):
     dist = dist_mod if world > 1 else None
     sampler = ClockSampler(local_rank)
     launches0 = _lib.launch_count()
-    ms, tokens, loss, peak_gb, mode = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist,
-                                                sampler, sd_prop=args.sd_prop, use_graph=not args.profile_mode)
+    tr = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist,
+                   sampler, sd_prop=args.sd_prop, use_graph=not args.profile_mode, primal_attention=args.primal_attention)
+    ms, tokens, loss, peak_gb, mode = tr["ms_per_step"], tr["tokens_per_step"], tr["loss"], tr["peak_mem_gb"], tr["launch"]
     launched = _lib.launch_count() - launches0
     tc = TRAIN_CONFIGS[args.workload]
     if rank == 0:
@@ -630,6 +715,7 @@ def main_train(args):
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 8 // world, "d2h_bytes_per_step": 4,
                     "note": "token ids come from pinned host memory and the loss goes back to the host every step"},
             "gpu_launches": int(launched), "loss": loss, "peak_mem_gb": peak_gb, "clocks": sampler.summary(),
+            "train": train_block(tr, world, peaks(), args.workload),
         }))
     if dist is not None:
         dist.barrier()

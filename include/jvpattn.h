@@ -41,7 +41,7 @@ enum {
   JVPATTN_EWORKSPACE = -6,/* workspace NULL or smaller than jvpattn_bwd_workspace_bytes()     */
   JVPATTN_EARCH = -7,     /* no CUDA device, or the device is not sm_100                      */
   JVPATTN_ELAUNCH = -8,   /* the CUDA runtime refused a launch; see jvpattn_last_cuda_error() */
-  JVPATTN_EDEVICE = -9,   /* a bounded device-side wait ran out; see jvpattn_device_status()  */
+  JVPATTN_EDEVICE = -9,   /* jvpattn_stream_check: a bounded device-side wait ran out; see jvpattn_device_status() */
   JVPATTN_ETOOLARGE = -10 /* jvpattn_bwd_static: problem larger than the built-in scratch     */
 };
 
@@ -74,15 +74,20 @@ typedef struct {
 /* Fused forward: O = softmax(scale QK^T) V together with its tangent Od along (tq, tk, tv), and the row
  * statistics lse = logsumexp(s) (the reference's M), mu = E_P[sd] (its MU); li (its LI, the softmax
  * denominator) is written only when non-NULL.  lse/mu/li are float32 [batch, heads, stat_len]; rows
- * >= len_q are not written.  o and to are written in place. */
+ * >= len_q are not written.  o and to are written in place.
+ * Primal-only form: with tq, tk, tv, to all NULL (mu may then be NULL too) the call is plain attention, O and lse
+ * only.  It stands in for the F.scaled_dot_product_attention call of the reference's non-JVP branch
+ * (semicat/net/duo.py:143-152); its backward is jvpattn_bwd with g_to = NULL.  Passing some but not all of the
+ * four is JVPATTN_EINVAL. */
 int jvpattn_fwd(const jvpattn_problem *p,
                 const jvpattn_tensor *q, const jvpattn_tensor *k, const jvpattn_tensor *v,
                 const jvpattn_tensor *tq, const jvpattn_tensor *tk, const jvpattn_tensor *tv,
                 const jvpattn_tensor *o, const jvpattn_tensor *to,
                 float *lse, float *mu, float *li, void *stream);
 
-/* Bytes of scratch jvpattn_bwd needs for this problem (row dot products and float32 accumulators for
- * dq / dtq).  Returns 0 for an invalid problem. */
+/* Bytes of scratch jvpattn_bwd needs for this problem: two float32 row vectors of batch * heads * stat_len
+ * elements each (the row dot products rowsum(g_to o O) and rowsum(g_to o Od) + rowsum(g_o o O)), rounded up to
+ * 256 bytes.  Returns 0 for an invalid problem. */
 size_t jvpattn_bwd_workspace_bytes(const jvpattn_problem *p);
 
 /* Backward: VJP of cotangents g_o (on O) and g_to (on Od) with respect to q, k, v, tq, tk, tv.
@@ -150,8 +155,25 @@ int jvpattn_profile_end(double *total_ms, uint64_t *launches);
 const char *jvpattn_kernel_name(int id);
 
 /* Synchronises the current device and returns the device-side status word: 0 if no bounded wait has
- * run out since the last call, else a code identifying the wait that gave up.  Clears the word. */
+ * run out since the last call, else a code identifying the wait that gave up (101..107 forward, 201..214
+ * backward).  Clears the word.  Every wait inside the kernels is bounded (about two seconds): a kernel whose
+ * wait runs out stops computing, leaves through its normal teardown and leaves its outputs unwritten or partial;
+ * the context stays usable. */
 int jvpattn_device_status(void);
+
+/* Waits for the work enqueued on `stream` and returns JVPATTN_EDEVICE if a device-side wait has run out since the
+ * status word was last cleared (the word is left in place for jvpattn_device_status), else JVPATTN_OK.  The
+ * reference has no counterpart: its Triton kernels contain no waits that could fail. */
+int jvpattn_stream_check(void *stream);
+
+/* Test hooks for the failure path (no counterpart in the reference; not for production use).
+ *   JVPATTN_DEBUG_WAIT_CYCLES     value = budget of every device-side wait in clock cycles for kernels launched from
+ *                                 now on; value <= 0 restores the default (about two seconds).
+ *   JVPATTN_DEBUG_STALL_NEXT_FWD  value != 0: in the next tcgen05 forward launch (only that one) the barrier of every
+ *                                 CTA's first key tile expects bytes that never arrive, so the waits behind it run out:
+ *                                 the kernel must end by itself, report a 10x status code and leave the device usable. */
+enum { JVPATTN_DEBUG_WAIT_CYCLES = 0, JVPATTN_DEBUG_STALL_NEXT_FWD = 1 };
+int jvpattn_debug_set(int knob, long long value);
 
 const char *jvpattn_strerror(int code);
 const char *jvpattn_last_cuda_error(void); /* text of the last CUDA runtime error seen by this thread */

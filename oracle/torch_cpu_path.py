@@ -47,18 +47,46 @@ def attention_jvp_with_grads(q, k, v, tq, tk, tv, g_o=None, g_od=None, scale=Non
     return o.detach(), od.detach(), grads
 
 
-def time_fwd_bwd(B, H, L, d, dtype=torch.float32, repeats=3, seed=0, threads=None):
-    """Best-of-``repeats`` wall time in seconds of one fwd+bwd (both cotangents) on the host cores."""
-    threads = threads or os.cpu_count() or 1
-    torch.set_num_threads(threads)
+def make_inputs(B, H, L, d, dtype=torch.float32, seed=0):
+    """Seeded inputs with the value distribution of the microbenchmark configuration, as a tuple
+    (q, k, v, tq, tk, tv, g_o, g_od)."""
     gen = torch.Generator().manual_seed(seed)
     mk = lambda s=1.0: (torch.randn(B, H, L, d, generator=gen) * s).to(dtype)
-    q, k, v = mk(1.0 / math.sqrt(d)), mk(), mk()
-    tq, tk, tv = mk(0.1), mk(0.1), mk(0.1)
-    g_o, g_od = mk(), mk()
+    return (mk(1.0 / math.sqrt(d)), mk(), mk(), mk(0.1), mk(0.1), mk(0.1), mk(), mk())
+
+
+def reference_attention_jvp():
+    """The reference's own ``naive_multihead_attention_jvp`` (semicat/jvp_utils/ryu_triton.py:426-454) from the
+    copy that ``oracle/make_ref.py`` makes, or ``None`` where that copy (or triton, which the module imports) is
+    absent.  Same call signature as :func:`attention_jvp` without ``scale``."""
+    import oracle
+    if oracle.import_reference() is None:
+        return None
+    try:
+        from semicat.jvp_utils.ryu_triton import naive_multihead_attention_jvp
+    except Exception:
+        return None
+    return naive_multihead_attention_jvp
+
+
+def fwd_bwd(inputs, attention=None):
+    """One forward (O, Od) and one backward (six VJPs, both cotangents) of ``attention`` (default: the
+    restatement in this file) on the host."""
+    fn = attention or attention_jvp
+    leaves = [x.detach().clone().requires_grad_(True) for x in inputs[:6]]
+    o, od = fn(*leaves)
+    return torch.autograd.grad([o, od], leaves, [inputs[6], inputs[7]])
+
+
+def time_fwd_bwd(B, H, L, d, dtype=torch.float32, repeats=3, seed=0, threads=None, attention=None):
+    """Best-of-``repeats`` wall time in seconds of one fwd+bwd (both cotangents) on the host cores.  The inputs
+    are drawn once, outside the timed region."""
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    inputs = make_inputs(B, H, L, d, dtype, seed)
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        attention_jvp_with_grads(q, k, v, tq, tk, tv, g_o, g_od)
+        fwd_bwd(inputs, attention)
         best = min(best, time.perf_counter() - t0)
     return best, threads

@@ -29,8 +29,9 @@ EXPORTS = (
     "jvpattn_fwd", "jvpattn_bwd", "jvpattn_bwd_workspace_bytes", "jvpattn_selected_kernels",
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
-    "jvpattn_bwd_static", "jvpattn_rotary_cast",
+    "jvpattn_bwd_static", "jvpattn_rotary_cast", "jvpattn_stream_check", "jvpattn_debug_set",
 )
+DEBUG_WAIT_CYCLES, DEBUG_STALL_NEXT_FWD = 0, 1
 STATIC_SCRATCH_ROWS = 262144
 NUM_KERNELS = 8
 
@@ -122,6 +123,10 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_launch_count.restype = ctypes.c_uint64
         lib.jvpattn_device_status.argtypes = []
         lib.jvpattn_device_status.restype = ctypes.c_int
+        lib.jvpattn_stream_check.argtypes = [ctypes.c_void_p]
+        lib.jvpattn_stream_check.restype = ctypes.c_int
+        lib.jvpattn_debug_set.argtypes = [ctypes.c_int, ctypes.c_longlong]
+        lib.jvpattn_debug_set.restype = ctypes.c_int
         lib.jvpattn_strerror.argtypes = [ctypes.c_int]
         lib.jvpattn_strerror.restype = ctypes.c_char_p
         lib.jvpattn_last_cuda_error.argtypes = []
@@ -156,6 +161,17 @@ def launch_count() -> int:
 
 def device_status() -> int:
     return int(load().jvpattn_device_status())
+
+
+def stream_check(stream: int | None = None) -> None:
+    """Wait for ``stream`` (default: the legacy default stream) and raise ``JvpAttnError(-9)`` if a device-side wait of
+    one of the kernels has run out; :func:`device_status` then tells which."""
+    check(load().jvpattn_stream_check(stream), "jvpattn_stream_check")
+
+
+def debug_set(knob: int, value: int) -> None:
+    """Test hooks of the failure path (``DEBUG_WAIT_CYCLES``, ``DEBUG_STALL_NEXT_FWD``); see include/jvpattn.h."""
+    check(load().jvpattn_debug_set(knob, value), "jvpattn_debug_set")
 
 
 def profile_begin() -> None:

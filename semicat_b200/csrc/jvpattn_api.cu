@@ -8,10 +8,14 @@
 #include <vector>
 
 #include "jvpattn_common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace jvpattn {
 
 static std::atomic<uint64_t> g_launches{0};
+// Test hooks (jvpattn_debug_set): the budget of the device-side waits and a one-shot injection for the next forward.
+static std::atomic<long long> g_wait_cycles{ptx::kWaitCycles};
+static std::atomic<int> g_inject_fwd{0};
 
 // ---- optional per-kernel timing (off by default; used by bench.py for the roofline figures)
 struct ProfSlot {
@@ -141,16 +145,26 @@ int build_fwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_t
   JVP_TRY(to_view(q, true, &a->q));
   JVP_TRY(to_view(k, true, &a->k));
   JVP_TRY(to_view(v, true, &a->v));
-  JVP_TRY(to_view(tq, true, &a->tq));
-  JVP_TRY(to_view(tk, true, &a->tk));
-  JVP_TRY(to_view(tv, true, &a->tv));
+  // tangents: all four of tq, tk, tv, to (and mu), or none of them (primal-only attention)
+  const bool any_t = (tq && tq->ptr) || (tk && tk->ptr) || (tv && tv->ptr) || (to && to->ptr);
+  JVP_TRY(to_view(tq, any_t, &a->tq));
+  JVP_TRY(to_view(tk, any_t, &a->tk));
+  JVP_TRY(to_view(tv, any_t, &a->tv));
   JVP_TRY(to_view(o, true, &a->o));
-  JVP_TRY(to_view(to, true, &a->to));
-  if (!lse || !mu) return JVPATTN_EINVAL;
+  JVP_TRY(to_view(to, any_t, &a->to));
+  if (!lse || (any_t && !mu)) return JVPATTN_EINVAL;
+  if (!any_t) {
+    // kernels that walk all six inputs (the portable ones) read the primals twice; nothing of it is written
+    a->tq = a->q; a->tk = a->k; a->tv = a->v;
+    mu = nullptr;
+  }
+  a->has_t = any_t ? 1 : 0;
   a->lse = lse; a->mu = mu; a->li = li;
   a->B = p->batch; a->H = p->heads; a->Lq = p->len_q; a->Lk = p->len_k; a->D = p->head_dim;
   a->stat_len = p->stat_len; a->dtype = p->dtype; a->scale = effective_scale(p);
   a->status = nullptr;
+  a->wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
+  a->inject = 0;
   return JVPATTN_OK;
 }
 
@@ -191,6 +205,7 @@ int build_bwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn_t
   a->B = p->batch; a->H = p->heads; a->Lq = p->len_q; a->Lk = p->len_k; a->D = p->head_dim;
   a->stat_len = p->stat_len; a->dtype = p->dtype; a->scale = effective_scale(p);
   a->workspace = nullptr; a->workspace_bytes = 0; a->status = nullptr;
+  a->wait_cycles = g_wait_cycles.load(std::memory_order_relaxed);
   return JVPATTN_OK;
 }
 
@@ -231,7 +246,7 @@ const char *jvpattn_strerror(int code) {
     case JVPATTN_EWORKSPACE: return "workspace missing or too small (see jvpattn_bwd_workspace_bytes)";
     case JVPATTN_EARCH: return "no usable CUDA device: this library runs on sm_100 (B200) only and has no CPU path";
     case JVPATTN_ELAUNCH: return "CUDA launch failed (see jvpattn_last_cuda_error)";
-    case JVPATTN_EDEVICE: return "a bounded device-side wait ran out";
+    case JVPATTN_EDEVICE: return "a bounded device-side wait ran out (jvpattn_device_status gives the code of the wait)";
     case JVPATTN_ETOOLARGE: return "problem exceeds the built-in scratch of jvpattn_bwd_static (batch*heads*stat_len > JVPATTN_STATIC_SCRATCH_ROWS); use jvpattn_bwd with a caller workspace";
     default: return "unknown jvpattn error code";
   }
@@ -294,6 +309,31 @@ int jvpattn_device_status(void) {
   return (int)word;
 }
 
+int jvpattn_stream_check(void *stream) {
+  DeviceInfo *d = nullptr;
+  int rc = current_device(&d);
+  if (rc != JVPATTN_OK) return rc;
+  unsigned int word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(&word, d->status, sizeof(word), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return note_cuda(e);
+  return word != 0 ? JVPATTN_EDEVICE : JVPATTN_OK;
+}
+
+int jvpattn_debug_set(int knob, long long value) {
+  switch (knob) {
+    case JVPATTN_DEBUG_WAIT_CYCLES:
+      g_wait_cycles.store(value > 0 ? value : ptx::kWaitCycles);
+      return JVPATTN_OK;
+    case JVPATTN_DEBUG_STALL_NEXT_FWD:
+      g_inject_fwd.store(value != 0 ? 1 : 0);
+      return JVPATTN_OK;
+    default:
+      return JVPATTN_EINVAL;
+  }
+}
+
 int jvpattn_selected_kernels(const jvpattn_problem *p, int which) {
   int rc = check_problem(p);
   if (rc != JVPATTN_OK) return rc;
@@ -329,6 +369,7 @@ int jvpattn_fwd(const jvpattn_problem *p, const jvpattn_tensor *q, const jvpattn
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   bool fast = p->kernels != JVPATTN_KERNELS_SIMT && sm100_fwd_supported(a);
   if (p->kernels == JVPATTN_KERNELS_TCGEN05 && !fast) return JVPATTN_EINVAL;
+  if (fast) a.inject = g_inject_fwd.exchange(0);  // one-shot test hook
   return note_cuda(fast ? sm100_fwd(a, s) : simt_fwd(a, s));
 }
 
@@ -397,6 +438,7 @@ int jvpattn_bwd_static(const jvpattn_problem *p, const jvpattn_tensor *q, const 
                        const jvpattn_tensor *dk, const jvpattn_tensor *dv, const jvpattn_tensor *dtq,
                        const jvpattn_tensor *dtk, const jvpattn_tensor *dtv, void *stream) {
   JVP_TRY(check_problem(p));
+  if (is_empty(p)) return JVPATTN_OK;
   const int64_t rows = (int64_t)p->batch * p->heads * p->stat_len;
   if (rows > JVPATTN_STATIC_SCRATCH_ROWS) return JVPATTN_ETOOLARGE;
   if (jvpattn_bwd_workspace_bytes(p) > sizeof(float) * 2 * JVPATTN_STATIC_SCRATCH_ROWS) return JVPATTN_ETOOLARGE;

@@ -24,6 +24,9 @@ struct FwdArgs {
   View q, k, v, tq, tk, tv, o, to;
   float *lse, *mu, *li;  // li may be null
   unsigned int *status;  // device status word, set when a bounded wait runs out
+  long long wait_cycles; // budget of every device-side wait, in clock cycles
+  int inject;            // test hook: 1 = the producer over-declares the bytes of the first key tile (its barrier never completes)
+  int has_t;             // 0: primal only (tq, tk, tv alias q, k, v; to.ptr and mu are null and not written)
   int B, H, Lq, Lk, D, stat_len;
   int dtype;
   float scale;
@@ -37,6 +40,7 @@ struct BwdArgs {
   void *workspace;
   size_t workspace_bytes;
   unsigned int *status;
+  long long wait_cycles;
   int B, H, Lq, Lk, D, stat_len;
   int dtype;
   float scale;

@@ -139,13 +139,13 @@ __global__ void __launch_bounds__(kWarps * 32) simt_fwd_kernel(FwdArgs a) {
       if (dd < D) {
         float o = acc[r][i] * inv;
         op[a.o.offset(b, h, row) + dd] = Elem<T>::from_f(o);
-        top[a.to.offset(b, h, row) + dd] = Elem<T>::from_f(gacc[r][i] * inv - mun * o);
+        if (top) top[a.to.offset(b, h, row) + dd] = Elem<T>::from_f(gacc[r][i] * inv - mun * o);  // null: primal only
       }
     }
     if (lane == 0) {
       size_t si = ((size_t)b * a.H + h) * a.stat_len + row;
       a.lse[si] = m[r] + __logf(l[r]);
-      a.mu[si] = mun;
+      if (a.mu) a.mu[si] = mun;
       if (a.li) a.li[si] = l[r];
     }
   }

@@ -25,8 +25,10 @@
 //
 //   warp 0      TMA producer (X once, Y through a 2-stage ring)
 //   warp 1      MMA issuer
-//   warps 2..9  two threads per owned row (each on half of the tile's columns): score algebra, operand
-//               write-back over consumed score columns, epilogue
+//   warps 2..   kParts threads per owned row (each on 1/kParts of the tile's columns): score algebra, operand
+//               write-back over consumed score columns, epilogue.  Four threads per row where a tile has 64
+//               columns (18 warps): the algebra is a chain of tensor-memory reads, exponentials and tensor-memory
+//               writes, and with two warps per scheduler its latency, not its instruction count, set the tile time
 #include <algorithm>
 
 #include "jvpattn_common.cuh"
@@ -39,8 +41,13 @@ namespace {
 using namespace ptx;
 
 constexpr int kRows = 128;
-constexpr int kThreads = 320;        // TMA warp, MMA warp, 8 score-algebra warps
-constexpr int kComputeThreads = 256;
+// threads of a CTA: TMA warp, MMA warp, 4 * parts score-algebra warps
+__host__ __device__ constexpr int bwd_threads(int parts) { return 64 + 128 * parts; }
+// score-algebra threads per owned row: each handles at least 16 columns of a streamed tile
+#ifndef JVPATTN_BWD_PARTS_WIDE
+#define JVPATTN_BWD_PARTS_WIDE 2
+#endif
+__host__ __device__ constexpr int bwd_parts(int tile) { return tile >= 64 ? JVPATTN_BWD_PARTS_WIDE : 2; }
 
 template <int D, int TILE>
 struct BwdSmem {
@@ -60,24 +67,6 @@ struct BwdSmem {
   uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done, vdone;
   uint32_t tmem_base;
 };
-
-// Optional event trace of CTA 0 (debug builds only: -DJVPATTN_TRACE): (tag, clock64) pairs.
-#ifdef JVPATTN_TRACE
-__device__ unsigned long long g_trace[2][9][1024];  // [query | key owner][MMA thread | lane 0 of each compute warp][event]
-#define JVP_TRACE_DECL(role) unsigned trace_n_ = 0; const int trace_role_ = (role)
-#define JVP_TRACE(tag)                                                                                        \
-  do {                                                                                                        \
-    if (blockIdx.x == 0 && trace_n_ < 1024)                                                                   \
-      g_trace[kKV ? 1 : 0][trace_role_][trace_n_++] = ((unsigned long long)(tag) << 48) | (clock64() & 0xFFFFFFFFFFFFull); \
-  } while (0)
-#else
-#define JVP_TRACE_DECL(role) \
-  do {                       \
-  } while (0)
-#define JVP_TRACE(tag) \
-  do {                 \
-  } while (0)
-#endif
 
 // Number of SMs of the current device (cached per device id).
 int sm_count() {
@@ -102,6 +91,7 @@ struct BwdKernelArgs {
   const float *lse, *mu;  // [B, H, stat_len]
   const float *delta, *dsum;
   unsigned int *status;
+  long long wait_cycles;           // budget of every bounded wait
   int B, H, Lx, Ly, Lq, stat_len;  // Lx rows on the owner side, Ly on the streamed side
   int xmask, ymask;             // which of the four X / Y tensors are loaded
   int has_t, has_o;
@@ -160,7 +150,9 @@ __global__ void __launch_bounds__(256) row_dots_kernel(BwdArgs a, float *delta, 
 }
 
 template <int D, int TILE, bool kKV, bool kDoK, bool kDoV, typename T>
-__global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_constant__ BwdMaps maps, BwdKernelArgs a) {
+__global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel(const __grid_constant__ BwdMaps maps, BwdKernelArgs a) {
+  constexpr int kParts = bwd_parts(TILE);
+  constexpr int kComputeThreads = 128 * kParts;
   extern __shared__ unsigned char smem_raw[];
   using Smem = BwdSmem<D, TILE>;
   Smem &s = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -177,7 +169,8 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   constexpr uint32_t kTmemCols = kUsed <= 256 ? 256 : 512;
   constexpr bool kBf16 = IsBf16<T>::value;
   constexpr uint32_t kTileBytes = TILE * D * 2;
-  constexpr int CH = TILE / 2;  // score columns per compute thread and tile
+  constexpr int CH = TILE / kParts;  // score columns per compute thread and tile
+  static_assert(CH % 16 == 0, "a compute thread reads its score columns 16 at a time");
   // d = 64 key owner: dV / dVd are final one group before dK / dKd (their last products are issued ahead of the last
   // tile's second half), so they are staged for the output stores while the tensor core finishes dK / dKd
   constexpr bool kEarlyV = kKV && kDoK && kDoV && kBoxes == 1;
@@ -245,7 +238,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         int b, h, x0;
         decode(it_, b, h, x0);
         const int xb = n_ % kXBuf;
-        if (!mbar_wait(&s.x_empty[xb], ((n_ / kXBuf) & 1) ^ 1)) {
+        if (!mbar_wait_for(a.wait_cycles, &s.x_empty[xb], ((n_ / kXBuf) & 1) ^ 1)) {
           atomicExch(a.status, 209u);
           return false;
         }
@@ -294,7 +287,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         if (kXBuf == 1 && n > 0 && !(ok = load_x(it, n))) break;
         for (int j = 0; j < ntiles; ++j, ++g) {
           const int st = g % kStages;
-          if (!mbar_wait(&s.y_empty[st], ((g / kStages) & 1) ^ 1)) {
+          if (!mbar_wait_for(a.wait_cycles, &s.y_empty[st], ((g / kStages) & 1) ^ 1)) {
             atomicExch(a.status, 201u);
             ok = false;
             break;
@@ -317,7 +310,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     //   outV(j):    dVd, dV += ...   needs compute1(j)         outK(j): dX1, dX0 += ...   needs compute2(j)
     // issue order: scores1(0) scores2(0) | outV(j) scores1(j+1) outK(j) scores2(j+1) | ...
     if (lane == 0) {
-      JVP_TRACE_DECL(0);
       constexpr uint32_t idesc_s = make_idesc(kRows, TILE, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kRows, D, kBf16, false, true);
       // Pairs of products that share their A operand and whose B tiles / accumulators are adjacent are issued as
@@ -346,7 +338,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       // last = this is the item's last tile (its X tiles are released once no later score MMA needs them)
       auto scores1 = [&](int g, int xb, bool last) -> bool {
         const int st = g % kStages;
-        if (!mbar_wait(&s.y_full[st], (g / kStages) & 1)) return false;
+        if (!mbar_wait_for(a.wait_cycles, &s.y_full[st], (g / kStages) & 1)) return false;
         tc_fence_after();
         const uint32_t xlo = xbase(xb), ylo = ybase(st);
         if (kMergeS && has_t) {
@@ -368,7 +360,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         tc_commit(&s.s1_full);
         if (!kDoK && last) tc_commit(&s.x_empty[xb]);
-        JVP_TRACE(1);
         return true;
       };
       auto scores2 = [&](int g, int xb, bool last) {
@@ -398,7 +389,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         tc_commit(&s.s2_full);
         if (last) tc_commit(&s.x_empty[xb]);
-        JVP_TRACE(6);
       };
       // Y tiles as MN-major B operands of the output products: consecutive 64-channel blocks are the two boxes of
       // one tensor (d = 128: four tiles apart) or, for the merged d = 64 products, two adjacent tensors
@@ -412,7 +402,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       // the stream of (item, tile) pairs this CTA walks; `n` counts items, `g` tiles
       int it = blockIdx.x, j = 0, n = 0, g = 0;
       bool ok = it < items;
-      if (ok && !mbar_wait(&s.x_full[0], 0)) {
+      if (ok && !mbar_wait_for(a.wait_cycles, &s.x_full[0], 0)) {
         atomicExch(a.status, 202u);
         ok = false;
       }
@@ -436,12 +426,11 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         const bool has_next = it2 < items;
         if (j == 0) init0 = init1 = initv = initvd = false;
-        if (!mbar_wait(&s.c1_done, g & 1)) {
+        if (!mbar_wait_for(a.wait_cycles, &s.c1_done, g & 1)) {
           atomicExch(a.status, 204u);
           break;
         }
-        JVP_TRACE(2);
-        if (j == 0 && !mbar_wait(&s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
+        if (j == 0 && !mbar_wait_for(a.wait_cycles, &s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
           atomicExch(a.status, 210u);
           break;
         }
@@ -479,7 +468,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         if (kEarlyV && j == ntiles - 1) tc_commit(&s.vdone);  // dV / dVd of this item are final
         if (has_next) {
-          if (j2 == 0 && !mbar_wait(&s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
+          if (j2 == 0 && !mbar_wait_for(a.wait_cycles, &s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
             atomicExch(a.status, 202u);
             break;
           }
@@ -489,11 +478,10 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           }
         }
         if (kDoK) {
-          if (!mbar_wait(&s.c2_done, g & 1)) {
+          if (!mbar_wait_for(a.wait_cycles, &s.c2_done, g & 1)) {
             atomicExch(a.status, 207u);
             break;
           }
-          JVP_TRACE(4);
           tc_fence_after();
           if (kMerge && has_t) {
             const bool acc = j > 0;
@@ -520,7 +508,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         }
         tc_commit(&s.y_empty[st]);
         if (j == ntiles - 1) tc_commit(&s.done);
-        JVP_TRACE(5);
         if (!has_next) break;
         scores2(g + 1, n2 % kXBuf, j2 == ntiles - 1);
         it = it2; j = j2; n = n2; ++g;
@@ -529,14 +516,10 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
   } else {
     // ------------------------------------------------------------------ score algebra: two threads per owned row
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int col0 = half * CH;
+    const int col0 = part * CH;
     const int ctid = threadIdx.x - 64;  // 0..255 among the compute threads
-#ifdef JVPATTN_TRACE
-    unsigned trace_n_ = lane == 0 ? 0u : 1024u;  // lane 0 of each compute warp records
-    const int trace_role_ = warp - 1;
-#endif
     const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
     const float sl2 = a.scale * kLog2e;
     const float2 sl2x2 = make_float2(sl2, sl2), scx2 = make_float2(a.scale, a.scale);
@@ -564,7 +547,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
     float4 rstat = make_float4(INFINITY, 0.f, 0.f, 0.f);  // row past the end: P = 0
     if (!kKV) {
       const int xb_ = n % kXBuf;
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.x_full[xb_], (n / kXBuf) & 1))) {
+      if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.x_full[xb_], (n / kXBuf) & 1))) {
         atomicExch(a.status, 211u);
         ok = false;
       }
@@ -577,15 +560,14 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
         if (ctid < TILE) s.stats[g & 1][ctid] = make_float4(pre.x * kLog2e, pre.y, pre.z, pre.w);
         if (j + 1 < ntiles) pre = fetch_stat(it, j + 1);
         else if (it + (int)gridDim.x < items) pre = fetch_stat(it + gridDim.x, 0);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
       }
       // a warp whose wait ran out keeps walking the loops without touching TMEM so that the barrier above still matches
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.s1_full, g & 1))) {
+      if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s1_full, g & 1))) {
         atomicExch(a.status, 205u);
         ok = false;
       }
       if (!ok) continue;
-      JVP_TRACE(10);
       tc_fence_after();
       const float4 *st = s.stats[g & 1];
       const int nvalid = a.Ly - j * TILE;  // streamed rows in this tile (masking for the query owner)
@@ -634,7 +616,6 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       if (kDoV) tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
-      JVP_TRACE(11);
       if (pending_xb >= 0) {
         // the previous item's output stores have long finished reading its X buffer: hand it back to the producer
         tma_store_wait_read();
@@ -643,12 +624,11 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       }
       if (!kDoK) continue;
       // ---- second half: W1 = scale P (A - delta), W2 = scale P ((A - delta) N + C - dsum)
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.s2_full, g & 1))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s2_full, g & 1))) {
         atomicExch(a.status, 208u);
         ok = false;
         continue;
       }
-      JVP_TRACE(12);
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < CH; c += 16) {
@@ -679,17 +659,18 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&s.c2_done);
-      JVP_TRACE(13);
     }
-    // ---- epilogue of the item: accumulators -> 16-bit outputs, each thread half of the channels of its row
+    // ---- epilogue of the item: accumulators -> 16-bit outputs, each thread 1/kParts of the channels of its row
     {
       const int xr = x0 + row;
       const bool live = xr < a.Lx;
-      const int cbase = half * (D / 2);
+      constexpr int kChan = D / kParts;  // channels per thread
+      const int cbase = part * kChan;
       auto store_acc = [&](uint32_t col, const View &v) {
+        static_assert(kBoxes == 1 || kChan % 32 == 0, "per-lane stores move 32 channels at a time");
         T *dst = static_cast<T *>(v.ptr) + v.offset(b, h, live ? xr : 0) + cbase;
 #pragma unroll
-        for (int c = 0; c < D / 2; c += 32) {
+        for (int c = 0; c < kChan; c += 32) {
           uint32_t r[32], pk[16];
           tmem_ld32(tlane + col + cbase + c, r);
           tc_wait_ld();
@@ -709,22 +690,27 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       // by every compute thread, whether or not its waits succeeded.
       const int xb = n % kXBuf;
       auto stage_acc = [&](uint32_t col, int which) {
-        uint32_t r[32];
-        tmem_ld32(tlane + col + cbase, r);
+        static_assert(kBoxes != 1 || kChan == 16 || kChan == 32, "staging moves 16 or 32 channels per thread");
+        uint32_t r[kChan];
+        if constexpr (kChan == 32) {
+          tmem_ld32(tlane + col + cbase, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        } else {
+          tmem_ld16(tlane + col + cbase, *reinterpret_cast<uint32_t(*)[16]>(&r[0]));
+        }
         tc_wait_ld();
         unsigned char *tile = reinterpret_cast<unsigned char *>(s.x[xb][which][0]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < kChan / 8; ++i) {
           uint4 v;
           v.x = pack2<T>(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
           v.y = pack2<T>(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
           v.z = pack2<T>(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
           v.w = pack2<T>(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-          *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, half * 4 + i)) = v;
+          *reinterpret_cast<uint4 *>(tile + swizzle128_offset(row, part * (kChan / 8) + i)) = v;
         }
       };
       if (kEarlyV) {
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.vdone, n & 1))) {
+        if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.vdone, n & 1))) {
           atomicExch(a.status, 214u);
           ok = false;
         }
@@ -734,11 +720,10 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           if (has_t) stage_acc(kColVd, 3);
         }
       }
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.done, n & 1))) {
+      if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.done, n & 1))) {
         atomicExch(a.status, 206u);
         ok = false;
       }
-      JVP_TRACE(14);
       tc_fence_after();
       if (kBoxes == 1) {
         const bool w0 = kDoK, w1 = kDoK && has_t, w2 = kDoV, w3 = kDoV && has_t;
@@ -749,7 +734,7 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
           if (w3 && !kEarlyV) stage_acc(kColVd, 3);
           fence_proxy_async();
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        asm volatile("bar.sync 2, %0;" ::"n"(kComputeThreads) : "memory");
         if (ctid == 0) {
           if (ok) {
             if (w0) tma_store_4d(&maps.out[0], s.x[xb][0][0], 0, x0, h, b);
@@ -772,12 +757,17 @@ __global__ void __launch_bounds__(kThreads) sm100_bwd_kernel(const __grid_consta
       }
       tc_fence_before();
       mbar_arrive(&s.acc_free);  // the next item may overwrite the accumulators
-      JVP_TRACE(15);
     }
    }  // items
   }
 
   if (threadIdx.x == 64) tma_store_wait_all();  // the thread that issued the output stores (nobody waits on x_empty any more)
+  // A key-owner grid may finish before the query-owner grid it was allowed to start beside.  Work that follows the
+  // call in the stream is ordered after this (the last) grid only, so one thread of every key-owner CTA waits for the
+  // grid before it here: the call's completion then implies the query owner's (and, at head_dim 128, the first key
+  // pass's).  Every CTA of the earlier grid is resident or done by the time a CTA of this one exists, so the wait
+  // cannot deadlock; it costs nothing unless this grid really is the faster one.
+  if (kKV && threadIdx.x == 32) griddep_wait();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
@@ -817,7 +807,7 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
           !make_tensor_map(&maps.out[t], ka.out[t].ptr, a.dtype, a.B, a.H, Lx, D, ka.out[t].sb, ka.out[t].sh, ka.out[t].sl, kRows))
         return cudaErrorInvalidValue;
   }
-  ka.lse = a.lse; ka.mu = a.mu; ka.delta = delta; ka.dsum = dsum; ka.status = a.status;
+  ka.lse = a.lse; ka.mu = a.mu; ka.delta = delta; ka.dsum = dsum; ka.status = a.status; ka.wait_cycles = a.wait_cycles;
   ka.B = a.B; ka.H = a.H; ka.Lx = Lx; ka.Ly = Ly; ka.Lq = a.Lq; ka.stat_len = a.stat_len;
   ka.has_t = has_t; ka.has_o = has_o; ka.scale = a.scale;
   auto kernel = sm100_bwd_kernel<D, TILE, kKV, kDoK, kDoV, T>;
@@ -828,7 +818,7 @@ cudaError_t launch_side(const BwdArgs &a, const float *delta, const float *dsum,
   dim3 grid((unsigned)std::min<int64_t>(items, sm_count()));  // persistent: one CTA per SM walks the items
   {
     LaunchScope scope(kKV ? kIdBwdKeyTc : kIdBwdQueryTc, stream);
-    e = launch_overlapped(kernel, grid, dim3(kThreads), smem, stream, maps, ka);
+    e = launch_overlapped(kernel, grid, dim3(bwd_threads(bwd_parts(TILE))), smem, stream, maps, ka);
   }
   return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -871,30 +861,17 @@ size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_l
   return (bytes + 255) / 256 * 256;
 }
 
-#ifdef JVPATTN_TRACE
-extern "C" int jvpattn_trace_read(unsigned long long *host) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
-  cudaMemset(nullptr, 0, 0);
-  static unsigned long long zeros[2][9][1024];
-  cudaMemcpyToSymbol(g_trace, zeros, sizeof(zeros));
-  return 0;
-}
-#endif
-
 bool sm100_bwd_supported(const BwdArgs &a) {
   if (a.D != 64 && a.D != 128) return false;
   if (a.Lq < 1 || a.Lk < 1 || a.H > 65535 || a.B > 65535) return false;
   const bool has_t = a.g_to.ptr != nullptr, has_o = a.g_o.ptr != nullptr;
-  const View *always[] = {&a.q, &a.k, &a.v, &a.o, &a.dq, &a.dk, &a.dv};
-  for (const View *v : always)
-    if (!tma_view_ok(*v, a.D)) return false;
-  if (has_t) {
-    const View *t[] = {&a.tq, &a.tk, &a.tv, &a.to, &a.g_to, &a.dtq, &a.dtk, &a.dtv};
-    for (const View *v : t)
-      if (!tma_view_ok(*v, a.D)) return false;
-  }
-  if (has_o && !tma_view_ok(a.g_o, a.D)) return false;
+  auto ok_q = [&](const View &v) { return tma_view_ok(v, a.B, a.H, a.Lq, a.D); };
+  auto ok_k = [&](const View &v) { return tma_view_ok(v, a.B, a.H, a.Lk, a.D); };
+  if (!ok_q(a.q) || !ok_q(a.o) || !ok_q(a.dq) || !ok_k(a.k) || !ok_k(a.v) || !ok_k(a.dk) || !ok_k(a.dv)) return false;
+  if (has_t && (!ok_q(a.tq) || !ok_q(a.to) || !ok_q(a.g_to) || !ok_q(a.dtq) || !ok_k(a.tk) || !ok_k(a.tv) || !ok_k(a.dtk) ||
+                !ok_k(a.dtv)))
+    return false;
+  if (has_o && !ok_q(a.g_o)) return false;
   // the query owner's row statistics travel by 16-byte-granular bulk copies
   if (reinterpret_cast<uintptr_t>(a.lse) % 16 || reinterpret_cast<uintptr_t>(a.workspace) % 16 || a.stat_len % 4) return false;
   if (has_t && reinterpret_cast<uintptr_t>(a.mu) % 16) return false;

@@ -12,6 +12,10 @@
 //
 // TMEM columns: [0,D) O, [D,2D) Od', [2D,2D+64) S / P, [2D+64,2D+128) Sd / U.  For D = 64 that is 256 columns
 // and under 100 KB of shared memory, so two CTAs share an SM and one's MMAs overlap the other's softmax.
+//
+// kHasT = false is the primal-only instance (no tangents given): the same pipeline without Qd, Kd, Vd, Sd, U and Od,
+// i.e. plain flash attention that writes O and lse.  It serves the callers' non-JVP attention (the reference uses
+// F.scaled_dot_product_attention there, semicat/net/duo.py:143-152) so that one kernel family covers the whole step.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -28,7 +32,12 @@ constexpr int kBM = 128;     // query rows per CTA (= TMEM lanes)
 constexpr int kBN = 64;      // keys per tile
 constexpr int kStages = 2;
 constexpr int kThreads = 192;
-constexpr float kRescaleThreshold = 8.0f;  // in log2 units: keep the old max while p stays below 2^8
+// Lazy rescale, in log2 units: the old reference maximum is kept while the new one is at most this far above it, so P
+// stays below 2^threshold and O / Od' need no rescale.  bf16 has the exponent range for 2^8; fp16 operands do not
+// (U = P o scale*sd would overflow for tangents 256 times smaller than with an exact maximum), so fp16 keeps the
+// exact running maximum, as the reference kernel does (ryu_triton.py:229-231).
+template <typename T> struct RescaleThreshold { static constexpr float value = 8.0f; };
+template <> struct RescaleThreshold<__half> { static constexpr float value = 0.0f; };
 
 template <int D>
 struct FwdSmem {
@@ -45,7 +54,7 @@ struct FwdMaps {
   CUtensorMap o, to;  // outputs as 128-row x 64-channel store boxes
 };
 
-template <int D, typename T>
+template <int D, typename T, bool kHasT>
 __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(const __grid_constant__ FwdMaps maps, FwdArgs a) {
   extern __shared__ unsigned char smem_raw[];
   using Smem = FwdSmem<D>;
@@ -73,18 +82,21 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     // key tiles are on their way while the other warps allocate tensor memory and meet at the barrier below.
     prefetch_tensormap(&maps.q);
     prefetch_tensormap(&maps.k);
-    mbar_expect_tx(&s.q_full, 2 * kBM * D * 2);
+    constexpr uint32_t kKvBytes = (kHasT ? 4 : 2) * kBN * D * 2;
+    mbar_expect_tx(&s.q_full, (kHasT ? 2 : 1) * kBM * D * 2);
     for (int x = 0; x < kBoxes; ++x) {
       tma_load_4d(s.q[x], &maps.q, &s.q_full, 64 * x, q0, h, b);
-      tma_load_4d(s.tq[x], &maps.tq, &s.q_full, 64 * x, q0, h, b);
+      if (kHasT) tma_load_4d(s.tq[x], &maps.tq, &s.q_full, 64 * x, q0, h, b);
     }
     for (int j = 0; j < ntiles && j < kStages; ++j) {
-      mbar_expect_tx(&s.kv_full[j], 4 * kBN * D * 2);
+      // (test hook: with `inject` the first tile's barrier expects 16 bytes that never arrive, so every role's wait
+      //  on it, or on what follows from it, runs out and the CTA leaves through the normal teardown)
+      mbar_expect_tx(&s.kv_full[j], kKvBytes + ((a.inject == 1 && j == 0) ? 16 : 0));
       for (int x = 0; x < kBoxes; ++x) {
         tma_load_4d(s.kv[j][0][x], &maps.k, &s.kv_full[j], 64 * x, j * kBN, h, b);
-        tma_load_4d(s.kv[j][1][x], &maps.tk, &s.kv_full[j], 64 * x, j * kBN, h, b);
+        if (kHasT) tma_load_4d(s.kv[j][1][x], &maps.tk, &s.kv_full[j], 64 * x, j * kBN, h, b);
         tma_load_4d(s.kv[j][2][x], &maps.v, &s.kv_full[j], 64 * x, j * kBN, h, b);
-        tma_load_4d(s.kv[j][3][x], &maps.tv, &s.kv_full[j], 64 * x, j * kBN, h, b);
+        if (kHasT) tma_load_4d(s.kv[j][3][x], &maps.tv, &s.kv_full[j], 64 * x, j * kBN, h, b);
       }
     }
   }
@@ -102,16 +114,16 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     if (lane == 0) {
       for (int j = kStages; j < ntiles; ++j) {  // the first kStages tiles were requested before the set-up barrier
         const int st = j % kStages;
-        if (!mbar_wait(&s.kv_empty[st], ((j / kStages) & 1) ^ 1)) {
+        if (!mbar_wait_for(a.wait_cycles, &s.kv_empty[st], ((j / kStages) & 1) ^ 1)) {
           atomicExch(a.status, 101u);
           break;
         }
-        mbar_expect_tx(&s.kv_full[st], 4 * kBN * D * 2);
+        mbar_expect_tx(&s.kv_full[st], (kHasT ? 4 : 2) * kBN * D * 2);
         for (int x = 0; x < kBoxes; ++x) {
           tma_load_4d(s.kv[st][0][x], &maps.k, &s.kv_full[st], 64 * x, j * kBN, h, b);
-          tma_load_4d(s.kv[st][1][x], &maps.tk, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          if (kHasT) tma_load_4d(s.kv[st][1][x], &maps.tk, &s.kv_full[st], 64 * x, j * kBN, h, b);
           tma_load_4d(s.kv[st][2][x], &maps.v, &s.kv_full[st], 64 * x, j * kBN, h, b);
-          tma_load_4d(s.kv[st][3][x], &maps.tv, &s.kv_full[st], 64 * x, j * kBN, h, b);
+          if (kHasT) tma_load_4d(s.kv[st][3][x], &maps.tv, &s.kv_full[st], 64 * x, j * kBN, h, b);
         }
       }
     }
@@ -127,11 +139,11 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
       constexpr uint32_t idesc_o2 = make_idesc(kBM, 2 * D <= 256 ? 2 * D : D, kBf16, false, true);
       const uint32_t base16 = smem_u32(&s) >> 4;
       constexpr uint32_t kQTile = kBM * 128, kKvTile = kBN * 128;  // bytes of one 64-channel box
-      bool ok = mbar_wait(&s.q_full, 0);
+      bool ok = mbar_wait_for(a.wait_cycles, &s.q_full, 0);
       if (!ok) atomicExch(a.status, 102u);
       for (int j = 0; ok && j < ntiles; ++j) {
         const int st = j % kStages;
-        if (!mbar_wait(&s.kv_full[st], (j / kStages) & 1)) {
+        if (!mbar_wait_for(a.wait_cycles, &s.kv_full[st], (j / kStages) & 1)) {
           atomicExch(a.status, 103u);
           break;
         }
@@ -146,7 +158,10 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         auto kd = [&](int t, int kk) {
           return kvlo + (uint32_t)(((t * kBoxes + (kk >> 2)) * kKvTile + (kk & 3) * 32) >> 4) + kDescLoKMajor;
         };
-        if (kMerge) {
+        if (!kHasT) {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(0, kk), idesc_s, kk > 0);
+        } else if (kMerge) {
           // [S | Sd] = Q [K ; Kd]^T in one N = 128 instruction per step, then Sd += Qd K^T
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) mma_ss_lo(tmem + kColS, qd(offsetof(Smem, q), kk), kd(0, kk), idesc_s2, kk > 0);
@@ -162,7 +177,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
           }
         }
         tc_commit(&s.s_full);
-        if (!mbar_wait(&s.p_full, j & 1)) {
+        if (!mbar_wait_for(a.wait_cycles, &s.p_full, j & 1)) {
           atomicExch(a.status, 104u);
           break;
         }
@@ -175,7 +190,9 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
           const uint32_t dv = kvlo + (uint32_t)((2 * kBoxes * kKvTile + kk * 2048) >> 4) + desc_lo_mn_major(kKvTile);
           const uint32_t dtv = kvlo + (uint32_t)((3 * kBoxes * kKvTile + kk * 2048) >> 4) + desc_lo_mn_major(kKvTile);
           const bool acc = (j > 0) || (kk > 0);
-          if (kMerge) {
+          if (!kHasT) {
+            mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o, acc);     // O += P V
+          } else if (kMerge) {
             mma_ts_lo(tmem + kColO, tmem + kColS + kk * 8, dv, idesc_o2, acc);    // [O | Od'] += P [V | Vd]
             mma_ts_lo(tmem + kColOd, tmem + kColSd + kk * 8, dv, idesc_o, true);  // Od' += U V
           } else {
@@ -198,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     bool ok = true;
     for (int j = 0; j < ntiles; ++j) {
       // tcgen05.ld / st are warp-collective: keep every decision that guards them warp-uniform
-      if (!__all_sync(0xffffffffu, mbar_wait(&s.s_full, j & 1))) {
+      if (!__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s_full, j & 1))) {
         atomicExch(a.status, 105u);
         ok = false;
         break;
@@ -211,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         uint32_t(&hi)[32] = *reinterpret_cast<uint32_t(*)[32]>(&sv[32]);
         tmem_ld32(tlane + kColS, lo);
         tmem_ld32(tlane + kColS + 32, hi);
-        tmem_ld32(tlane + kColSd, sd);
+        if (kHasT) tmem_ld32(tlane + kColSd, sd);
         tc_wait_ld();
       }
       const int nvalid = a.Lk - j * kBN;  // >= 1; < 64 only on the last tile
@@ -228,14 +245,14 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         for (int t = 0; t < 4; ++t) mx4[t] = fmaxf(mx4[t], __uint_as_float(sv[c + t]));
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
-      // Keep the old reference max while the new one is at most 2^8 above it: O / Od' then need no rescale.
-      float m_new = (mx - m > kRescaleThreshold) ? mx : m;
+      // Keep the old reference max while the new one is within the threshold above it: O / Od' then need no rescale.
+      float m_new = (mx - m > RescaleThreshold<T>::value) ? mx : m;
       if (j == 0) m_new = mx;
       const float alpha = fast_exp2(m - m_new);  // 1 when unchanged, 0 on the first tile
       if (j > 0 && __any_sync(0xffffffffu, m_new != m)) {
         // S of this tile is complete, so every earlier O / Od' update has retired: safe to rescale in place.
 #pragma unroll
-        for (int c = 0; c < 2 * D; c += 32) {
+        for (int c = 0; c < (kHasT ? 2 : 1) * D; c += 32) {
           uint32_t r[32];
           tmem_ld32(tlane + kColO + c, r);
           tc_wait_ld();
@@ -252,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t pk[16], uk[16];
-        if (c0 > 0) {
+        if (kHasT && c0 > 0) {
           tmem_ld32(tlane + kColSd + c0, sd);
           tc_wait_ld();
         }
@@ -260,16 +277,18 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         for (int i = 0; i < 16; ++i) {
           const float2 t = __ffma2_rn(make_float2(__uint_as_float(sv[c0 + 2 * i]), __uint_as_float(sv[c0 + 2 * i + 1])), sl2x2, negm);
           const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-          const float2 u = __fmul2_rn(__fmul2_rn(p, scx2),
-                                      make_float2(__uint_as_float(sd[2 * i]), __uint_as_float(sd[2 * i + 1])));
           psum[i & 1] = __fadd2_rn(psum[i & 1], p);
-          usum[i & 1] = __fadd2_rn(usum[i & 1], u);
           pk[i] = pack2<T>(p.x, p.y);
-          uk[i] = pack2<T>(u.x, u.y);
+          if (kHasT) {
+            const float2 u = __fmul2_rn(__fmul2_rn(p, scx2),
+                                        make_float2(__uint_as_float(sd[2 * i]), __uint_as_float(sd[2 * i + 1])));
+            usum[i & 1] = __fadd2_rn(usum[i & 1], u);
+            uk[i] = pack2<T>(u.x, u.y);
+          }
         }
         // 32 score columns become 16 packed operand columns, written over columns already consumed
         tmem_st16(tlane + kColS + c0 / 2, pk);
-        tmem_st16(tlane + kColSd + c0 / 2, uk);
+        if (kHasT) tmem_st16(tlane + kColSd + c0 / 2, uk);
       }
       l = l * alpha + ((psum[0].x + psum[0].y) + (psum[1].x + psum[1].y));
       mu = mu * alpha + ((usum[0].x + usum[0].y) + (usum[1].x + usum[1].y));
@@ -278,7 +297,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
       mbar_arrive(&s.p_full);
     }
     // ---- epilogue: O = acc / l ; Od = Od'/l - (mu/l) O ; statistics
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(&s.o_done, (ntiles - 1) & 1))) {
+    if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.o_done, (ntiles - 1) & 1))) {
       atomicExch(a.status, 106u);
       ok = false;
     }
@@ -294,7 +313,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
       for (int c = 0; c < D; c += 32) {
         uint32_t ro[32], rd[32];
         tmem_ld32(tlane + kColO + c, ro);
-        tmem_ld32(tlane + kColOd + c, rd);
+        if (kHasT) tmem_ld32(tlane + kColOd + c, rd);
         tc_wait_ld();
         unsigned char *otile = reinterpret_cast<unsigned char *>(s.q[c / 64]);
         unsigned char *dtile = reinterpret_cast<unsigned char *>(s.tq[c / 64]);
@@ -306,18 +325,19 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
             const int e = 8 * i + 2 * t;
             const float o0 = __uint_as_float(ro[e]) * inv, o1 = __uint_as_float(ro[e + 1]) * inv;
             po[t] = pack2<T>(o0, o1);
-            pd[t] = pack2<T>(__uint_as_float(rd[e]) * inv - mun * o0, __uint_as_float(rd[e + 1]) * inv - mun * o1);
+            if (kHasT)
+              pd[t] = pack2<T>(__uint_as_float(rd[e]) * inv - mun * o0, __uint_as_float(rd[e + 1]) * inv - mun * o1);
           }
           const uint32_t off = swizzle128_offset(row, (c % 64) / 8 + i);
           *reinterpret_cast<uint4 *>(otile + off) = make_uint4(po[0], po[1], po[2], po[3]);
-          *reinterpret_cast<uint4 *>(dtile + off) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
+          if (kHasT) *reinterpret_cast<uint4 *>(dtile + off) = make_uint4(pd[0], pd[1], pd[2], pd[3]);
         }
       }
       fence_proxy_async();
       if (live) {
         const size_t si = ((size_t)b * a.H + h) * a.stat_len + qrow;
         a.lse[si] = m * kLn2 + __logf(l);
-        a.mu[si] = mun;
+        if (kHasT) a.mu[si] = mun;
         if (a.li) a.li[si] = l;
       }
     }
@@ -325,7 +345,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     if (threadIdx.x == 64 && ok) {
       for (int x = 0; x < kBoxes; ++x) {
         tma_store_4d(&maps.o, s.q[x], 64 * x, q0, h, b);
-        tma_store_4d(&maps.to, s.tq[x], 64 * x, q0, h, b);
+        if (kHasT) tma_store_4d(&maps.to, s.tq[x], 64 * x, q0, h, b);
       }
       tma_store_commit();
       tma_store_wait_read();  // the tiles must stay until the stores have read them; the writes finish on their own
@@ -337,18 +357,19 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
   if (warp == 1) tmem_dealloc(tmem, kTmemCols);
 }
 
-template <int D, typename T>
+template <int D, typename T, bool kHasT>
 cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
   FwdMaps maps;
   const View *views[8] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv, &a.o, &a.to};
   CUtensorMap *dst[8] = {&maps.q, &maps.tq, &maps.k, &maps.tk, &maps.v, &maps.tv, &maps.o, &maps.to};
   for (int i = 0; i < 8; ++i) {
+    if (!kHasT && (i & 1)) continue;  // the tangent-side tensors are absent
     const bool is_q = i < 2 || i >= 6;
     if (!make_tensor_map(dst[i], views[i]->ptr, a.dtype, a.B, a.H, is_q ? a.Lq : a.Lk, D, views[i]->sb, views[i]->sh,
                          views[i]->sl, is_q ? kBM : kBN))
       return cudaErrorInvalidValue;
   }
-  auto kernel = sm100_fwd_kernel<D, T>;
+  auto kernel = sm100_fwd_kernel<D, T, kHasT>;
   const size_t smem = sizeof(FwdSmem<D>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
@@ -365,16 +386,21 @@ cudaError_t launch_fwd(const FwdArgs &a, cudaStream_t stream) {
 bool sm100_fwd_supported(const FwdArgs &a) {
   if (a.D != 64 && a.D != 128) return false;
   if (a.Lq < 1 || a.Lk < 1 || a.H > 65535 || a.B > 65535) return false;
-  const View *views[8] = {&a.q, &a.tq, &a.k, &a.tk, &a.v, &a.tv, &a.o, &a.to};
-  for (const View *v : views)
-    if (!tma_view_ok(*v, a.D)) return false;
+  const View *qside[4] = {&a.q, &a.o, &a.tq, &a.to}, *kside[4] = {&a.k, &a.v, &a.tk, &a.tv};
+  const int n = a.has_t ? 4 : 2;  // the tangent-side views exist only with tangents
+  for (int i = 0; i < n; ++i)
+    if (!tma_view_ok(*qside[i], a.B, a.H, a.Lq, a.D) || !tma_view_ok(*kside[i], a.B, a.H, a.Lk, a.D)) return false;
   return true;
 }
 
+template <typename T>
+cudaError_t dispatch_fwd(const FwdArgs &a, cudaStream_t stream) {
+  if (a.has_t) return a.D == 64 ? launch_fwd<64, T, true>(a, stream) : launch_fwd<128, T, true>(a, stream);
+  return a.D == 64 ? launch_fwd<64, T, false>(a, stream) : launch_fwd<128, T, false>(a, stream);
+}
+
 cudaError_t sm100_fwd(const FwdArgs &a, cudaStream_t stream) {
-  if (a.dtype == JVPATTN_BF16)
-    return a.D == 64 ? launch_fwd<64, __nv_bfloat16>(a, stream) : launch_fwd<128, __nv_bfloat16>(a, stream);
-  return a.D == 64 ? launch_fwd<64, __half>(a, stream) : launch_fwd<128, __half>(a, stream);
+  return a.dtype == JVPATTN_BF16 ? dispatch_fwd<__nv_bfloat16>(a, stream) : dispatch_fwd<__half>(a, stream);
 }
 
 }  // namespace jvpattn

@@ -34,11 +34,13 @@ template <typename T> struct IsBf16 { static constexpr bool value = false; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr bool value = true; };
 
 // A view the TMA / vector-store paths can take: 16-byte aligned base, strides that keep every row 16-byte
-// aligned, rows that do not overlap.
-inline bool tma_view_ok(const View &v, int D) {
+// aligned, rows that do not overlap, and a positive stride below 2^40 bytes on every axis that has more than one
+// entry (a tensor map cannot describe a broadcast axis; an expanded tensor takes the SIMT kernels instead).
+inline bool tma_view_ok(const View &v, int B, int H, int L, int D) {
   if (!v.ptr) return false;
   if (reinterpret_cast<uintptr_t>(v.ptr) % 16 != 0) return false;
-  return v.sl % 8 == 0 && v.sh % 8 == 0 && v.sb % 8 == 0 && v.sl >= D;
+  auto axis_ok = [](int64_t stride, int n) { return n <= 1 || (stride > 0 && stride % 8 == 0 && stride < (int64_t(1) << 39)); };
+  return axis_ok(v.sl, L) && axis_ok(v.sh, H) && axis_ok(v.sb, B) && (L <= 1 || v.sl >= D);
 }
 
 }  // namespace jvpattn

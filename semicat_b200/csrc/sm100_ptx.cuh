@@ -40,16 +40,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 
-// About two seconds at B200 clocks; a healthy wait in these kernels lasts microseconds.
+// Default budget of a wait: about two seconds at B200 clocks; a healthy wait in these kernels lasts microseconds.
+// The budget travels with the kernel arguments (jvpattn_debug_set can shorten it for the failure-path test).
 constexpr long long kWaitCycles = 4000000000LL;
 
-// Bounded wait.  Returns false when the budget ran out (the caller then records a status code and
-// leaves through the kernel's normal teardown).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+// Bounded wait.  Returns false when `limit` clock cycles went by without the barrier completing the phase (the
+// caller then records a status code and leaves through the kernel's normal teardown).
+__device__ __forceinline__ bool mbar_wait_for(long long limit, uint64_t *bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }

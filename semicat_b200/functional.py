@@ -6,8 +6,7 @@ Contract kept from the reference (semicat/jvp_utils/functional.py):
 * ``sdpa_jvp(q, k, v)`` takes (B, H, S, D) fp16/bf16 CUDA tensors and is meant to be called under
   forward-mode AD (``torch.func.jvp`` around the model, semicat/models/semicat.py:132-136, 153-157).
   The plain ``forward`` only hands out the output buffer and the row-statistic buffer; the fused
-  kernel fills both when autograd calls ``jvp`` (functional.py:216-258).  Called without forward-mode
-  AD the output is uninitialised, exactly as in the reference (functional.py:286-287).
+  kernel fills both when autograd calls ``jvp`` (functional.py:216-258).
 * The result is then reverse-mode differentiable with respect to q, k, v AND their tangents: a
   cotangent on the tangent output runs the JVP backward (functional.py:71-87, 90-168), a cotangent on
   the primal output runs the plain attention backward (functional.py:171-213, 260-268); autograd sums
@@ -18,12 +17,25 @@ Contract kept from the reference (semicat/jvp_utils/functional.py):
 Differences, all internal: one library call per pass instead of 1 + 6 + 2 Triton launches; the
 LI buffer (softmax denominator) of the reference is not produced because no kernel here needs it;
 the tangent output is not zero-filled before the kernel writes it.
+
+One extension: when none of q, k, v carries a forward-mode tangent, ``sdpa_jvp`` runs the primal-only instance
+of the same kernels (plain attention, reverse-mode differentiable) instead of returning an uninitialised buffer.
+The callers' non-JVP attention (the reference uses ``F.scaled_dot_product_attention`` there,
+semicat/net/duo.py:143-152) can therefore go through this library too.
+
+When both outputs receive a cotangent in one reverse pass (the ``ecld`` objective, semicat/models/semicat.py:131-151),
+autograd calls the two backward methods below separately, as it does with the reference's two Functions: two
+library calls, and autograd adds the two (dq, dk, dv) contributions.  The single merged call that handles both
+cotangents at once (``ops.jvp_attention_bwd`` with ``g_o`` and ``g_to``) is available to direct callers only: the
+tangent-side gradients must be returned by the node autograd visits first, before the cotangent of the primal output
+is known to it.
 """
 from __future__ import annotations
 
 import math
 
 import torch
+import torch.autograd.forward_ad as fwAD
 from torch.autograd.function import once_differentiable
 
 from . import ops
@@ -130,6 +142,34 @@ class _Attention(torch.autograd.Function):
         return dq, dk, dv
 
 
+class _PrimalAttention(torch.autograd.Function):
+    """Plain attention through the primal-only kernel instance; used when no input carries a tangent."""
+
+    @staticmethod
+    def forward(ctx, q, k, v):
+        B, H, S, _ = q.shape
+        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+        q, k, v = fix(q), fix(k), fix(v)
+        y = torch.empty((B, S, H, v.shape[-1]), dtype=q.dtype, device=q.device).transpose(1, 2)
+        lse = torch.empty((B, H, ops.stat_len(S)), dtype=torch.float32, device=q.device)
+        ops.jvp_attention_fwd(q, k, v, None, None, None, y, None, lse, None, kernels=_kernels)
+        ctx.save_for_backward(q, k, v, y, lse)
+        return y
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, g_y):
+        q, k, v, y, lse = ctx.saved_tensors
+        g_y = g_y if g_y.stride(-1) == 1 else g_y.contiguous()
+        dq, dk, dv = (_like_input(t) for t in (q, k, v))
+        ops.jvp_attention_bwd(q, k, v, None, None, None, y, None, g_y, None, lse, None, dq, dk, dv, kernels=_kernels)
+        return dq, dk, dv
+
+
+def _carries_tangent(t: torch.Tensor) -> bool:
+    return fwAD.unpack_dual(t).tangent is not None
+
+
 def _validate(q, k, v):
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
         raise ValueError("sdpa_jvp expects 4-D (B, H, S, D) tensors")
@@ -151,9 +191,13 @@ def sdpa_jvp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Fused scaled-dot-product attention that supports forward-mode AD; (B, H, S, D) in and out.
 
     Use as ``y, ty = torch.func.jvp(sdpa_jvp, (q, k, v), (tq, tk, tv))`` or call it inside a model that
-    is itself wrapped in ``torch.func.jvp``.  Without forward-mode AD the result is uninitialised.
+    is itself wrapped in ``torch.func.jvp``.  Without forward-mode AD (no input carries a tangent) the call is
+    plain attention through the primal-only kernels, differentiable in reverse mode (the reference returns an
+    uninitialised buffer in that case, functional.py:286-287).
     """
     _validate(q, k, v)
+    if not (_carries_tangent(q) or _carries_tangent(k) or _carries_tangent(v)):
+        return _PrimalAttention.apply(q, k, v)
     y, _ = _Attention.apply(q, k, v)
     return y
 

@@ -84,8 +84,12 @@ class _on_device:
 
 
 def jvp_attention_fwd(q, k, v, tq, tk, tv, o, to, lse, mu, li=None, scale=None, kernels=KERNELS_AUTO):
-    """Fill ``o``, ``to``, ``lse``, ``mu`` (and ``li`` if given) in place.  All 4-D tensors are (B, H, L, D)."""
+    """Fill ``o``, ``to``, ``lse``, ``mu`` (and ``li`` if given) in place.  All 4-D tensors are (B, H, L, D).
+    With ``tq``, ``tk``, ``tv``, ``to`` (and ``mu``) all ``None`` the call is primal-only attention: ``o`` and
+    ``lse`` alone are written."""
     lib = _lib.load()
+    if (tq is None) != (tk is None) or (tq is None) != (tv is None) or (tq is None) != (to is None):
+        raise ValueError("pass all of tq, tk, tv, to or none of them")
     _check_shapes(q, k, [("tq", tq), ("o", o), ("to", to)], [("k", k), ("v", v), ("tk", tk), ("tv", tv)])
     B, H, Lq, _ = q.shape
     prob = _problem(q, k, lse.shape[-1], scale, kernels)
@@ -94,7 +98,7 @@ def jvp_attention_fwd(q, k, v, tq, tk, tv, o, to, lse, mu, li=None, scale=None, 
             (("q", q), ("k", k), ("v", v), ("tq", tq), ("tk", tk), ("tv", tv), ("o", o), ("to", to))]
     stat_shape = (B, H, lse.shape[-1])
     with _on_device(dev):
-        rc = lib.jvpattn_fwd(ctypes.byref(prob), *[ctypes.byref(a) for a in args],
+        rc = lib.jvpattn_fwd(ctypes.byref(prob), *[ctypes.byref(a) if a is not None else None for a in args],
                              _fptr(lse, "lse", stat_shape, dev), _fptr(mu, "mu", stat_shape, dev),
                              _fptr(li, "li", stat_shape, dev), torch.cuda.current_stream(dev).cuda_stream)
     _lib.check(rc, "jvpattn_fwd")

@@ -2,8 +2,9 @@
 step that pushes ``torch.func.jvp`` through it.
 
 This is NOT part of the kernel library; it exists so that ``bench.py`` can report DiT JVP-training
-tokens/s on the reference's architecture without the reference checkout (which does not travel to the
-GPU box) and without Lightning/Hydra.  Architecture and objective follow the reference:
+tokens/s on the reference's architecture without depending on the reference package, Lightning or Hydra.
+:func:`load_reference_state` copies the parameters of a reference ``DIT`` into this restatement (the tests use it
+to check the two models against each other).  Architecture and objective follow the reference:
 
 * denoiser: semicat/net/duo.py:299-360 (``DIT``), blocks :101-166 (LayerNorm, adaLN modulation with
   zero-initialised projection, bias-free qkv, rotary on q and k in fp32, attention through
@@ -96,7 +97,9 @@ class Block(nn.Module):
             v = v.to(rot_dtype)
         else:
             q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
-        if attention == "jvp":
+        if attention in ("jvp", "lib"):
+            # the library's kernels: fused JVP attention where the inputs carry forward-mode tangents, the primal-only
+            # instance of the same kernels where they do not ("lib" names that use in the non-JVP passes)
             a = safe_sdpa_jvp(q, k, v)
         elif attention == "math":  # plain formula: supports forward-mode AD anywhere (used by the CPU tests)
             qh, kh, vh = (z.transpose(1, 2).float() for z in (q, k, v))
@@ -166,6 +169,34 @@ class DiT(nn.Module):
         return _aligned_linear(self.norm_out(h) * (1.0 + scale) + shift, self.head)
 
 
+_REFERENCE_NAMES = (  # prefix in semicat/net/duo.py's DIT -> prefix here
+    ("vocab_embed.film_gamma.", "embed.gamma."), ("vocab_embed.film_beta.", "embed.beta."),
+    ("vocab_embed.final_norm.", "embed.norm."), ("vocab_embed.", "embed."),
+    ("output_layer.norm_final.", "norm_out."), ("output_layer.adaLN_modulation.", "ada_out."),
+    ("output_layer.linear.", "head."), (".adaLN_modulation.", ".ada."),
+)
+
+
+def load_reference_state(net: "DiT", reference_state: dict) -> None:
+    """Copy the parameters of a reference ``semicat.net.duo.DIT`` (its ``state_dict()``) into ``net``.
+    The rotary tables are buffers computed from the shape on both sides and are not copied."""
+    mapped = {}
+    for name, value in reference_state.items():
+        if name.startswith("rotary_emb."):
+            continue
+        for old, new in _REFERENCE_NAMES:
+            if old in name:
+                name = name.replace(old, new)
+                break
+        mapped[name] = value
+    own = net.state_dict()
+    missing = [k for k in own if k not in mapped and k not in ("cos", "sin")]
+    extra = [k for k in mapped if k not in own]
+    if missing or extra:
+        raise KeyError(f"reference state does not match: missing {missing}, unexpected {extra}")
+    net.load_state_dict(mapped, strict=False)
+
+
 def randomise_zero_init(net: nn.Module, std=0.05, seed=0):
     """A freshly built DiT multiplies its attention branch by zero gates; parity tests un-zero them first."""
     g = torch.Generator().manual_seed(seed)
@@ -197,8 +228,12 @@ def draw_noise(x1, vocab, generator=None):
             "u_sd": torch.rand(B, device=dev, generator=generator)}
 
 
-def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0):
-    """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L)."""
+def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0,
+               primal_attention="sdpa"):
+    """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L).
+    ``jvp_attention`` selects the attention of the forward-mode pass, ``primal_attention`` that of the passes without
+    tangents (the cross-entropy step and the no-grad target): "sdpa" is ``F.scaled_dot_product_attention`` as in the
+    reference (semicat/net/duo.py:143-152), "lib" this library's primal-only kernels, "math" the plain formula."""
     B = x1.shape[0]
     split = int(sd_prop * B)
     dev_type = x1.device.type
@@ -210,7 +245,7 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
         t = noise["t_vfm"][split:]
         xt = interpolate(x0[split:], x1[split:], t.view(-1, 1, 1))
         with ac():
-            pred = net(xt, t, t)
+            pred = net(xt, t, t, attention=primal_attention)
         # Same value as the reference's F.cross_entropy(pred.transpose(-1, 1), x1) (semicat.py:107-111): mean over all
         # tokens.  With the classes innermost the log-softmax over the 30522-entry vocabulary runs as a row softmax;
         # in the transposed (B, V, L) layout it is a strided "spatial" softmax that took a third of the whole step.
@@ -225,7 +260,7 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
         xst, dv = torch.func.jvp(lambda _t: flow_map(net, xs, s, _t, jvp_attention), (t,), (torch.ones_like(t),))
         xst = xst.detach()
         with torch.no_grad():
-            target = net(xst, t, t).softmax(dim=-1)
+            target = net(xst, t, t, attention=primal_attention).softmax(dim=-1)
     sd_loss = ((1.0 - t).view(-1, 1, 1) * dv - target + xst).pow(2).sum(dim=-1).mean()
     return vf_loss, sd_loss
 

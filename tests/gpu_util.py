@@ -131,3 +131,25 @@ def compare(got, want, mode, label):
         for n in GRAD_NAMES:
             if n in got:
                 assert_close(got[n], want[n], f"{label}:{n}")
+
+
+def oracle_rows(inputs, mode="both", scale=None, rows=1024):
+    """The fp64 oracle evaluated in chunks of query rows, for sequences whose (L x L) score matrices would not
+    fit at once.  Attention rows are independent, so outputs and query-side gradients are per chunk and the
+    key-side gradients are sums over chunks."""
+    Lq = inputs["q"].shape[2]
+    parts = []
+    acc = None
+    for r0 in range(0, Lq, rows):
+        sl = slice(r0, min(r0 + rows, Lq))
+        sub = {n: (x[:, :, sl] if n in ("q", "tq", "g_o", "g_od") else x) for n, x in inputs.items()}
+        out = oracle(sub, mode, scale)
+        parts.append(out)
+        if mode is not None:
+            ksum = {n: out[n] for n in ("dk", "dv", "dtk", "dtv")}
+            acc = ksum if acc is None else {n: acc[n] + ksum[n] for n in acc}
+    res = {n: np.concatenate([p[n] for p in parts], axis=2) for n in ("o", "to", "lse", "mu")}
+    if mode is not None:
+        res.update({n: np.concatenate([p[n] for p in parts], axis=2) for n in ("dq", "dtq")})
+        res.update(acc)
+    return res

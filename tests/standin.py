@@ -19,12 +19,16 @@ def _put(dst, arr):
 
 
 def fwd(q, k, v, tq, tk, tv, o, to, lse, mu, li=None, scale=None, kernels=0):
+    primal_only = tq is None
+    if primal_only:
+        tq, tk, tv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
     O, Od, LSE, MU = closed_form.forward(*map(_np, (q, k, v, tq, tk, tv)), scale=scale)
     _put(o, O)
-    _put(to, Od)
     L = q.shape[2]
     lse.data[..., :L] = torch.from_numpy(LSE).float()
-    mu.data[..., :L] = torch.from_numpy(MU).float()
+    if not primal_only:
+        _put(to, Od)
+        mu.data[..., :L] = torch.from_numpy(MU).float()
 
 
 def bwd(q, k, v, tq, tk, tv, o, to, g_o, g_to, lse, mu, dq, dk, dv, dtq=None, dtk=None, dtv=None,

@@ -75,3 +75,15 @@ def test_no_device_means_earch_not_a_fallback(lib):
     r = ctypes.byref
     assert lib.jvpattn_fwd(r(p), *[r(t)] * 8, 0x1000, 0x1000, None, None) == -7
     assert lib.jvpattn_launch_count() == 0
+
+
+@pytest.mark.parametrize("B,H,Lq", [(1, 1, 128), (64, 12, 128), (3, 5, 200), (8, 16, 8192), (2, 2, 1)])
+def test_backward_scratch_is_two_row_vectors(lib, B, H, Lq):
+    """jvpattn_bwd_static's fixed array and its row limit rely on the workspace being exactly two fp32 vectors of
+    batch * heads * stat_len entries (rounded up to 256 bytes): a workspace that grew would silently shrink that limit."""
+    stat = (Lq + 127) // 128 * 128
+    for D in (16, 64, 128):
+        p = _prob(batch=B, heads=H, len_q=Lq, len_k=Lq, head_dim=D, stat_len=stat)
+        need = lib.jvpattn_bwd_workspace_bytes(ctypes.byref(p))
+        assert need == (8 * B * H * stat + 255) // 256 * 256
+    assert 8 * _lib.STATIC_SCRATCH_ROWS == 2 * 1024 * 1024

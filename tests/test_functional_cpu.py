@@ -95,3 +95,28 @@ def test_validate_messages(monkeypatch):
     q = torch.zeros(1, 1, 8, 32, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU path"):
         torch.func.jvp(functional.sdpa_jvp, (q, q, q), (q, q, q))
+
+
+def test_without_tangents_the_call_is_plain_attention():
+    """No input carries a forward-mode tangent: the primal-only path runs (the reference hands back an
+    uninitialised buffer there) and is reverse-mode differentiable."""
+    g = load_golden("c1_fp32")
+    q, k, v = (torch.from_numpy(g[n]).requires_grad_(True) for n in ("q", "k", "v"))
+    o = functional.sdpa_jvp(q, k, v)
+    np.testing.assert_allclose(o.detach().numpy(), g["o"], rtol=1e-4, atol=1e-4)
+    grads = torch.autograd.grad(o, (q, k, v), torch.from_numpy(g["g_o"]))
+    for n, got in zip(("dq", "dk", "dv"), grads):
+        np.testing.assert_allclose(got.numpy(), g[f"{n}_pri"], rtol=1e-4, atol=1e-4)
+    # the safe wrapper takes the same route, in the (B, S, H, D) layout (fp32 inputs pass through bf16 there)
+    o2 = functional.safe_sdpa_jvp(*(t.detach().transpose(1, 2).contiguous() for t in (q, k, v)))
+    assert o2.dtype == torch.float32
+    np.testing.assert_allclose(o2.transpose(1, 2).numpy(), g["o"], rtol=2e-2, atol=2e-2)
+
+
+def test_tangent_on_one_input_only_takes_the_jvp_path():
+    g = load_golden("selftest_1")
+    q, k, v, tq, tk, tv = _leaves(g)
+    o, to = torch.func.jvp(lambda v_: functional.sdpa_jvp(q.detach(), k.detach(), v_), (v.detach(),), (tv.detach(),))
+    o3, to3 = torch.func.jvp(functional.sdpa_jvp, (q.detach(), k.detach(), v.detach()),
+                             (torch.zeros_like(q), torch.zeros_like(k), tv.detach()))
+    assert torch.allclose(o, o3) and torch.allclose(to, to3)

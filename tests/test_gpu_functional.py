@@ -60,3 +60,27 @@ def test_output_buffers_keep_their_autograd_version():
     o, to = torch.func.jvp(sdpa_jvp, tuple(leaves[:3]), tuple(leaves[3:]))
     (o.float().square().sum() + to.float().square().sum()).backward()
     assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in leaves)
+
+
+def test_without_tangents_the_public_entry_points_run_plain_attention():
+    """No forward-mode tangent on any input: sdpa_jvp / safe_sdpa_jvp go through the primal-only kernels and are
+    reverse-mode differentiable (the reference returns an uninitialised buffer here, functional.py:286-287)."""
+    ins = G.rounded(G.synth(2, 3, 256, 256, 64, seed=8), torch.bfloat16)
+    q, k, v = (torch.as_tensor(ins[n]).to("cuda", torch.bfloat16).requires_grad_(True) for n in ("q", "k", "v"))
+    before = _lib.launch_count()
+    o = sdpa_jvp(q, k, v)
+    assert _lib.launch_count() == before + 1
+    want = G.oracle(ins, "pri")
+    G.assert_close(o.detach().float().cpu().numpy(), want["o"], "o")
+    grads = torch.autograd.grad(o, (q, k, v), torch.as_tensor(ins["g_o"]).to("cuda", torch.bfloat16))
+    for n, g in zip(("dq", "dk", "dv"), grads):
+        G.assert_close(g.float().cpu().numpy(), want[n], n)
+    # (B, S, H, D) wrapper with fp32 inputs
+    q2, k2, v2 = (t.detach().float().transpose(1, 2).contiguous() for t in (q, k, v))
+    o2 = safe_sdpa_jvp(q2, k2, v2)
+    assert o2.dtype == torch.float32 and o2.shape == q2.shape
+    G.assert_close(o2.transpose(1, 2).cpu().numpy(), want["o"], "o (safe wrapper)")
+    # a tangent on a single input still takes the fused path
+    o3, to3 = torch.func.jvp(lambda v_: sdpa_jvp(q.detach(), k.detach(), v_), (v.detach(),), (v.detach(),))
+    assert torch.equal(o3, o.detach())  # zero tangents on q, k; P V with tv = v gives Od = O
+    G.assert_close(to3.float().cpu().numpy(), want["o"], "Od with tv = v equals O")

@@ -160,3 +160,145 @@ def test_backward_launch_overlap_is_ordered(shape):
         want = G.oracle(ins, "both")
         for gn in G.GRAD_NAMES:
             G.assert_close(got[gn], want[gn], f"overlap/{shape}/{gn}")
+
+
+@pytest.mark.parametrize("Lq,Lk", [(4096, 128), (128, 4096)])
+def test_graph_replay_orders_the_consumer_after_every_backward_kernel(Lq, Lk):
+    """The key-owner kernels may run beside the query-owner kernel and, with few key rows, finish long before it.
+    Work that follows the call must still see dq / dtq complete, also when the call is replayed from a CUDA graph
+    (where only the edges between consecutive kernels exist): a copy kernel that reads every gradient follows the
+    backward inside the graph, and its result must equal the eager one bit for bit on every replay."""
+    B, H, D = 2, 4, 64
+    dt = torch.bfloat16
+    ins = G.rounded(G.synth(B, H, Lq, Lk, D, seed=13), dt)
+    t = {n: G.place(ins[n], dt, "bshd") for n in G.IN_NAMES}
+    g_o, g_to = G.place(ins["g_o"], dt, "bshd"), G.place(ins["g_od"], dt, "bshd")
+    o, to = torch.empty_like(t["q"]), torch.empty_like(t["q"])
+    lse = torch.zeros(B, H, ops.stat_len(Lq), dtype=torch.float32, device="cuda")
+    mu = torch.zeros_like(lse)
+    ops.jvp_attention_fwd(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], o, to, lse, mu)
+    grads = [torch.empty_like(t[n]) for n in G.IN_NAMES]
+    ws = ops.jvp_attention_bwd(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], o, to, g_o, g_to, lse, mu, *grads)
+    torch.cuda.synchronize()
+    eager = [g.clone() for g in grads]
+    want = G.oracle(ins, "both")
+    for gn, x in zip(G.GRAD_NAMES, eager):
+        G.assert_close(x.float().cpu().numpy(), want[gn], f"Lq{Lq} Lk{Lk}:{gn}")
+    copies = [torch.zeros_like(g) for g in grads]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ops.jvp_attention_bwd(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], o, to, g_o, g_to, lse, mu, *grads,
+                                  workspace=ws)
+            for c, g in zip(copies, grads):
+                c.copy_(g)
+    torch.cuda.current_stream().wait_stream(side)
+    for r in range(6):
+        for g in grads:
+            g.fill_(float("nan"))  # a consumer that ran early would pick these up
+        graph.replay()
+        torch.cuda.synchronize()
+        for gn, c, e in zip(G.GRAD_NAMES, copies, eager):
+            assert torch.equal(c, e), f"replay {r}: {gn} read before it was complete"
+    assert _lib.device_status() == 0
+
+
+def test_broadcast_views_fall_back_to_the_portable_kernels():
+    """An expanded (stride 0) tangent cannot be described by a TMA tensor map: the automatic choice must run it on
+    the SIMT kernels instead of failing at launch."""
+    B, H, L, D = 2, 3, 128, 64
+    dt = torch.bfloat16
+    ins = G.rounded(G.synth(B, H, L, L, D, seed=17), dt)
+    ins["tk"] = np.zeros_like(ins["tk"])
+    t = {n: G.place(ins[n], dt, "bhld") for n in G.IN_NAMES}
+    t["tk"] = torch.zeros(1, 1, L, D, dtype=dt, device="cuda").expand(B, H, L, D)
+    o, to = torch.empty_like(t["q"]), torch.empty_like(t["q"])
+    lse = torch.zeros(B, H, L, dtype=torch.float32, device="cuda")
+    mu = torch.zeros_like(lse)
+    ops.jvp_attention_fwd(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], o, to, lse, mu)
+    grads = [torch.empty(B, H, L, D, dtype=dt, device="cuda") for _ in range(6)]
+    g_o, g_to = G.place(ins["g_o"], dt, "bhld"), G.place(ins["g_od"], dt, "bhld")
+    ops.jvp_attention_bwd(t["q"], t["k"], t["v"], t["tq"], t["tk"], t["tv"], o, to, g_o, g_to, lse, mu, *grads)
+    torch.cuda.synchronize()
+    want = G.oracle(ins, "both")
+    got = {"o": o, "to": to, "lse": lse, "mu": mu, **dict(zip(G.GRAD_NAMES, grads))}
+    G.compare({n: x.float().cpu().numpy() for n, x in got.items()}, want, "both", "expanded tangent")
+
+
+def test_fp16_large_tangents_with_rising_scores():
+    """fp16 operands overflow at 65504: with scores that rise from key tile to key tile and tangents of magnitude
+    ~30, a stale softmax reference maximum would push P o sd past that.  The fp16 kernels keep the exact running
+    maximum (as the reference kernel does), so the result stays finite and within tolerance."""
+    B, H, L, D = 1, 2, 512, 64
+    dt = torch.float16
+    ins = G.synth(B, H, L, L, D, seed=23, q_scale=1.0, t_scale=30.0)
+    # keys grow along the sequence, so every 64-key tile brings a larger row maximum than the one before
+    ramp = np.linspace(0.2, 1.6, L, dtype=np.float32)[None, None, :, None]
+    ins["q"] = np.abs(ins["q"]) * 0.5
+    ins["k"] = np.abs(ins["k"]) * ramp
+    ins = G.rounded(ins, dt)
+    got = G.run(ins, dtype=dt, mode=None)
+    want = G.oracle(ins, None)
+    assert np.isfinite(got["to"]).all()
+    G.compare(got, want, None, "fp16 large tangents")
+
+
+@pytest.mark.parametrize("family", list(FAMILIES))
+@pytest.mark.parametrize("shape", [(2, 3, 256, 256, 64), (1, 2, 384, 200, 128), (1, 2, 200, 72, 32), (64, 12, 128, 128, 64)])
+def test_primal_only_forward_and_its_backward(shape, family):
+    """No tangents: plain attention through the primal-only kernel instance.  O and lse must equal the oracle's (and
+    the fused call's with zero tangents, bit for bit on the tensor-core path), the tangent-side buffers must stay
+    untouched, and the 'pri' backward on its outputs must match the oracle."""
+    B, H, Lq, Lk, D = shape
+    dt = torch.bfloat16
+    ins = G.rounded(G.synth(B, H, Lq, Lk, D, seed=31), dt)
+    t = {n: G.place(ins[n], dt, "bshd") for n in ("q", "k", "v")}
+    o_buf, o, pad, n_o = G.guarded_like(t["q"])
+    stat = ops.stat_len(Lq)
+    lse = torch.full((B, H, stat), G.CANARY, dtype=torch.float32, device="cuda")
+    ops.jvp_attention_fwd(t["q"], t["k"], t["v"], None, None, None, o, None, lse, None, kernels=FAMILIES[family])
+    G.check_canaries(o_buf, pad, n_o, "o")
+    sel = (slice(0, B, 21), slice(0, H, 5)) if B * H > 16 else (slice(None), slice(None))
+    sub = {n: x[sel] for n, x in ins.items()}
+    want = G.oracle(sub, "pri")
+    G.assert_close(o[sel].float().cpu().numpy(), want["o"], f"{shape}/{family}:o")
+    G.assert_close(lse[..., :Lq][sel].cpu().numpy(), want["lse"], f"{shape}/{family}:lse", rtol=1e-3, atol=2e-3)
+    if Lq < stat:
+        assert bool((lse[..., Lq:] == G.CANARY).all())
+    # against the fused call with zero tangents
+    z = {n: torch.zeros_like(t[m]) for n, m in (("tq", "q"), ("tk", "k"), ("tv", "v"))}
+    o2, to2 = torch.empty_like(o), torch.empty_like(o)
+    lse2, mu2 = torch.empty_like(lse), torch.empty_like(lse)
+    ops.jvp_attention_fwd(t["q"], t["k"], t["v"], z["tq"], z["tk"], z["tv"], o2, to2, lse2, mu2, kernels=FAMILIES[family])
+    assert torch.equal(o, o2) and torch.equal(lse[..., :Lq], lse2[..., :Lq])
+    # backward of the primal output alone
+    g_o = G.place(ins["g_o"], dt, "bshd")
+    grads = [torch.empty_like(t[n]) for n in ("q", "k", "v")]
+    ops.jvp_attention_bwd(t["q"], t["k"], t["v"], None, None, None, o, None, g_o, None, lse, None, *grads,
+                          kernels=FAMILIES[family])
+    torch.cuda.synchronize()
+    for gn, x in zip(("dq", "dk", "dv"), grads):
+        G.assert_close(x[sel].float().cpu().numpy(), want[gn], f"{shape}/{family}:{gn}")
+    assert _lib.device_status() == 0
+
+
+def test_primal_only_against_fp32_math_attention():
+    B, H, L, D = 2, 4, 512, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q, k, v = (torch.randn(B, H, L, D, device="cuda", generator=g).bfloat16() for _ in range(3))
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, dtype=torch.float32, device="cuda")
+    ops.jvp_attention_fwd(q, k, v, None, None, None, o, None, lse, None)
+    s = (q.float() @ k.float().transpose(-1, -2)) / D ** 0.5
+    want = torch.softmax(s, dim=-1) @ v.float()
+    G.assert_close(o.float().cpu().numpy(), want.cpu().numpy(), "primal-only vs fp32 math attention")
+    G.assert_close(lse.cpu().numpy(), torch.logsumexp(s, dim=-1).cpu().numpy(), "lse", rtol=1e-3, atol=2e-3)
+
+
+def test_partial_tangent_set_is_refused():
+    q = torch.zeros(1, 1, 128, 64, dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros(1, 1, 128, dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        ops.jvp_attention_fwd(q, q, q, q, None, None, q.clone(), None, lse, None)
