@@ -24,7 +24,8 @@
 // tensor core as the A operand; the Y tiles are read MN-major as the B operand.
 //
 //   warp 0      TMA producer (X once, Y through a 2-stage ring)
-//   warp 1      MMA issuer
+//   warp 1      MMA issuer (query owner: the score products)
+//   last warp   query owner only: second MMA issuer (the output products)
 //   warps 2..   kParts threads per owned row (each on 1/kParts of the tile's columns): score algebra, operand
 //               write-back over consumed score columns, epilogue.  Four threads per row where a tile has 64
 //               columns (18 warps): the algebra is a chain of tensor-memory reads, exponentials and tensor-memory
@@ -41,8 +42,8 @@ namespace {
 using namespace ptx;
 
 constexpr int kRows = 128;
-// threads of a CTA: TMA warp, MMA warp, 4 * parts score-algebra warps
-__host__ __device__ constexpr int bwd_threads(int parts) { return 64 + 128 * parts; }
+// threads of a CTA: TMA warp, MMA warp, 4 * parts score-algebra warps, and the second MMA warp of the query owner
+__host__ __device__ constexpr int bwd_threads(int parts) { return 64 + 128 * parts + 32; }
 // score-algebra threads per owned row: each handles at least 16 columns of a streamed tile
 #ifndef JVPATTN_BWD_PARTS_WIDE
 #define JVPATTN_BWD_PARTS_WIDE 2
@@ -64,9 +65,10 @@ struct BwdSmem {
   // flight holds a scoreboard slot that the tensor-memory reads of the score algebra also wait on, which exposed
   // the memory latency once per item even with nothing depending on the load.
   alignas(16) float xstat[kXBuf][4][kRows];
-  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, done, vdone;
+  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, r2_free, done, vdone;
   uint32_t tmem_base;
 };
+
 
 // Number of SMs of the current device (cached per device id).
 int sm_count() {
@@ -164,7 +166,12 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
   constexpr uint32_t kColVd = kDoK ? 2 * D : 0, kColV = kColVd + D;  // dVd, dV
   // two score regions that are in different phases of the pipeline: (S | Sd) and (A | C)
   constexpr uint32_t kColS = kAcc * D, kColSd = kColS + TILE, kColA = kColS + 2 * TILE, kColC = kColS + 3 * TILE;
-  constexpr uint32_t kUsed = kAcc * D + 4 * TILE;
+  // Query owner: its two accumulators leave room for a separate, double-buffered home of the W1 / W2 operands
+  // (TILE / 2 packed columns each), so that the (A | C) region is free again as soon as the score algebra has read it
+  // instead of when the output products have consumed the operands written over it.
+  constexpr bool kSplit = !kKV;
+  constexpr uint32_t kColW = kAcc * D + 4 * TILE;
+  constexpr uint32_t kUsed = kColW + (kSplit ? 2 * TILE : 0);
   static_assert(kUsed <= 512, "TMEM budget");
   constexpr uint32_t kTmemCols = kUsed <= 256 ? 256 : 512;
   constexpr bool kBf16 = IsBf16<T>::value;
@@ -176,6 +183,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
   constexpr bool kEarlyV = kKV && kDoK && kDoV && kBoxes == 1;
 
   constexpr int kXBuf = Smem::kXBuf;
+  constexpr int kWarpB = 2 + 4 * kParts;  // the second MMA issuer sits behind the score-algebra warps
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int ntiles = (a.Ly + TILE - 1) / TILE;
   const bool has_t = a.has_t != 0, has_o = a.has_o != 0;
@@ -204,6 +212,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
     mbar_init(&s.s2_full, 1);
     mbar_init(&s.c1_done, kComputeThreads);
     mbar_init(&s.c2_done, kComputeThreads);
+    mbar_init(&s.r2_free, kComputeThreads);
     mbar_init(&s.done, 1);
     mbar_init(&s.vdone, 1);
     fence_barrier_init();
@@ -301,7 +310,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == kWarpB) {
     // ------------------------------------------------------------------ MMA issuer
     // Per streamed tile j the tensor core runs four groups, interleaved with the two halves of the score
     // algebra so that it always has the next group queued while the compute warps work:
@@ -309,7 +318,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
     //   scores2(j): A, C             -> compute2(j): W1, W2 (operands)
     //   outV(j):    dVd, dV += ...   needs compute1(j)         outK(j): dX1, dX0 += ...   needs compute2(j)
     // issue order: scores1(0) scores2(0) | outV(j) scores1(j+1) outK(j) scores2(j+1) | ...
-    if (lane == 0) {
+    if (lane == 0 && (warp == 1 || kSplit)) {
       constexpr uint32_t idesc_s = make_idesc(kRows, TILE, kBf16, false, false);
       constexpr uint32_t idesc_o = make_idesc(kRows, D, kBf16, false, true);
       // Pairs of products that share their A operand and whose B tiles / accumulators are adjacent are issued as
@@ -399,6 +408,108 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       // the thread that owned score columns [16 kk, 16 kk + 16) left its 8 packed operand columns at the start
       // of its own column range (see the score-algebra warps)
       auto oa = [&](int kk) -> uint32_t { return ((16 * kk) / CH) * CH + ((16 * kk) % CH) / 2; };
+      if constexpr (kSplit) {
+        // ---- query owner: two issuers and a chain-free schedule.
+        // Measured per 64-key tile with one issuer: the score algebra needed ~1570 cycles, the tensor pipe ~1280, but a
+        // tile took ~3280, because (A | C) of the next tile could only be issued behind the output products of this
+        // one (which read W1 / W2 from that region), and those wait for the second half of the score algebra: a serial
+        // chain of algebra -> 8 MMAs -> 8 MMAs -> algebra, with every tcgen05.commit on the way holding back its
+        // thread's later MMAs until the earlier ones have drained.  Here W1 / W2 have a home of their own, so
+        //   issuer A (warp 1):    scores1(j+1) once compute1(j) has read (S | Sd); scores2(j+1) once compute2(j) has
+        //                         read (A | C) - neither waits for an output product;
+        //   issuer B (last warp): outK(j) once compute2(j) has written W1 / W2; its commits (stage free, item done)
+        //                         drain only its own queue.
+        // Hazards: W[g & 1] is rewritten by compute2(g + 2), which needs scores2(g + 2), which needs the streamed
+        // stage of tile g reloaded, which needs outK(g) complete (y_empty): outK(g) has long read it.
+        int it = blockIdx.x, j = 0, n = 0, g = 0;
+        bool ok = it < items;
+        if (warp == 1) {
+          if (ok && !mbar_wait_for(a.wait_cycles, &s.x_full[0], 0)) {
+            atomicExch(a.status, 202u);
+            ok = false;
+          }
+          if (ok) {
+            if (!scores1(0, 0, false)) {
+              atomicExch(a.status, 203u);
+              ok = false;
+            } else {
+              scores2(0, 0, ntiles == 1);
+            }
+          }
+          while (ok) {
+            int it2 = it, j2 = j + 1, n2 = n;
+            if (j2 == ntiles) {
+              it2 = it + gridDim.x;
+              j2 = 0;
+              n2 = n + 1;
+            }
+            if (it2 >= items) break;
+            if (!mbar_wait_for(a.wait_cycles, &s.c1_done, g & 1)) {  // (S | Sd) of tile g has been read
+              atomicExch(a.status, 204u);
+              break;
+            }
+            if (j2 == 0 && !mbar_wait_for(a.wait_cycles, &s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
+              atomicExch(a.status, 202u);
+              break;
+            }
+            if (!scores1(g + 1, n2 % kXBuf, false)) {
+              atomicExch(a.status, 203u);
+              break;
+            }
+            if (!mbar_wait_for(a.wait_cycles, &s.r2_free, g & 1)) {  // (A | C) of tile g has been read
+              atomicExch(a.status, 207u);
+              break;
+            }
+            tc_fence_after();
+            scores2(g + 1, n2 % kXBuf, j2 == ntiles - 1);
+            it = it2; j = j2; n = n2; ++g;
+          }
+        } else {
+          const bool acc_merge = kMerge && has_t;
+          for (; ok; ) {
+            const int st = g % kStages;
+            if (!mbar_wait_for(a.wait_cycles, &s.c2_done, g & 1)) {  // W1 / W2 of tile g are in place
+              atomicExch(a.status, 207u);
+              break;
+            }
+            if (j == 0 && !mbar_wait_for(a.wait_cycles, &s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
+              atomicExch(a.status, 210u);
+              break;
+            }
+            tc_fence_after();
+            const uint32_t ylo_out = ybase(st);
+            const uint32_t w1 = tmem + kColW + (uint32_t)(g & 1) * TILE, w2 = w1 + TILE / 2;
+            if (acc_merge) {
+              const bool acc = j > 0;
+#pragma unroll
+              for (int kk = 0; kk < TILE / 16; ++kk) {
+                mma_ts_lo(tmem + kColKd, w1 + 8 * kk, yb(ylo_out, 0, kk), idesc_o2, acc || kk > 0);  // [dX1 | dX0] += W1 [Y0 | Y1]
+                mma_ts_lo(tmem + kColK, w2 + 8 * kk, yb(ylo_out, 0, kk), idesc_o, true);          // dX0 += W2 Y0
+              }
+            } else {
+#pragma unroll
+              for (int kk = 0; kk < TILE / 16; ++kk) {
+                bool init0 = j > 0 || kk > 0;
+                if (has_t) {
+                  mma_ts_lo(tmem + kColKd, w1 + 8 * kk, yb(ylo_out, 0, kk), idesc_o, init0);   // dX1 += W1 Y0
+                  mma_ts_lo(tmem + kColK, w1 + 8 * kk, yb(ylo_out, 1, kk), idesc_o, init0);    // dX0 += W1 Y1
+                  init0 = true;
+                }
+                mma_ts_lo(tmem + kColK, w2 + 8 * kk, yb(ylo_out, 0, kk), idesc_o, init0);      // dX0 += W2 Y0
+              }
+            }
+            tc_commit(&s.y_empty[st]);
+            if (j == ntiles - 1) tc_commit(&s.done);
+            if (++j == ntiles) {
+              it += gridDim.x;
+              j = 0;
+              ++n;
+            }
+            ++g;
+            if (it >= items) break;
+          }
+        }
+      } else {
       // the stream of (item, tile) pairs this CTA walks; `n` counts items, `g` tiles
       int it = blockIdx.x, j = 0, n = 0, g = 0;
       bool ok = it < items;
@@ -512,6 +623,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         scores2(g + 1, n2 % kXBuf, j2 == ntiles - 1);
         it = it2; j = j2; n = n2; ++g;
       }
+      }  // single issuer
     }
   } else {
     // ------------------------------------------------------------------ score algebra: two threads per owned row
@@ -580,6 +692,11 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         tmem_ld16(tlane + kColS + cs, rs);
         if (has_t) tmem_ld16(tlane + kColSd + cs, rd);
         tc_wait_ld();
+        if (!kDoV && c + 16 >= CH) {
+          // nothing is written back over the scores: the region is free once this thread's last read has landed
+          tc_fence_before();
+          mbar_arrive(&s.c1_done);
+        }
         if (!kKV && nvalid < TILE) {
 #pragma unroll
           for (int i = 0; i < 16; ++i)
@@ -613,9 +730,11 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
           if (has_t) tmem_st8(tlane + kColSd + col0 + c / 2, kpn);
         }
       }
-      if (kDoV) tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
+      if (kDoV) {
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(&s.c1_done);  // S / Sd consumed (the region may be refilled) and P / PoN in place
+      }
       if (pending_xb >= 0) {
         // the previous item's output stores have long finished reading its X buffer: hand it back to the producer
         tma_store_wait_read();
@@ -637,6 +756,10 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         if (has_t) tmem_ld16(tlane + kColA + cs, ra);
         tmem_ld16(tlane + kColC + cs, rc);
         tc_wait_ld();
+        if (kSplit && c + 16 >= CH) {
+          tc_fence_before();
+          mbar_arrive(&s.r2_free);  // (A | C) read: the next tile's products may overwrite the region
+        }
         uint32_t kw1[8], kw2[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -653,8 +776,15 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
           const float2 w2 = __fmul2_rn(sp[c / 2 + i], inner);
           kw2[i] = pack2<T>(w2.x, w2.y);
         }
-        if (has_t) tmem_st8(tlane + kColA + col0 + c / 2, kw1);
-        tmem_st8(tlane + kColC + col0 + c / 2, kw2);
+        if (kSplit) {
+          // contiguous packing in the operands' own buffer: key column k of the tile sits in packed column k / 2
+          const uint32_t wbase = tlane + kColW + (uint32_t)(g & 1) * TILE + (col0 + c) / 2;
+          if (has_t) tmem_st8(wbase, kw1);
+          tmem_st8(wbase + TILE / 2, kw2);
+        } else {
+          if (has_t) tmem_st8(tlane + kColA + col0 + c / 2, kw1);
+          tmem_st8(tlane + kColC + col0 + c / 2, kw2);
+        }
       }
       tc_wait_st();
       tc_fence_before();
