@@ -455,6 +455,71 @@ def cpu_path(cfg, repeats, threads=None):
     return best, used, kind
 
 
+def run_triton_comparator(args):
+    """`--impl reference_triton`: the reference's own GPU path (its Triton kernels behind semicat.jvp_utils.functional.sdpa_jvp,
+    JIT-compiled by the installed Triton for this GPU) timed with the same inputs and the same CUDA-event harness, forward
+    and backward separately, on config 2 and on a B4 H16 L2048 d64 slice of the long-sequence sweep.  A comparator and a
+    second parity opinion only; needs the copy of the reference package made by oracle/make_ref.py.  Any failure to
+    import, compile or run is reported as text in the JSON line instead of a number."""
+    import torch
+    import oracle
+    out = {"impl": "reference_triton", "metric": "jvp_attn_fwd_bwd_tflops", "unit": "TFLOP/s", "rows": []}
+    try:
+        if oracle.import_reference() is None:
+            raise RuntimeError("no copy of the reference package (run oracle/make_ref.py where the reference checkout is)")
+        import triton
+        from semicat.jvp_utils import functional as ref_functional
+        out["triton"] = triton.__version__
+    except Exception as e:
+        out["unavailable"] = f"{type(e).__name__}: {e}"[:400]
+        print(json.dumps(out))
+        return
+    from semicat_b200 import functional as ours
+    dev = torch.device("cuda", 0)
+    for name in ("config2", "L2048_d64_small"):
+        cfg = WORKLOADS[name]
+        B, H, L, D = cfg["B"], cfg["H"], cfg["L"], cfg["D"]
+        host = host_inputs(cfg, seed=0)
+        t = {n: x.to(dev).transpose(1, 2) for n, x in host.items()}  # (B,H,L,D) views of (B,S,H,D) memory
+        row = {"workload": name, "shape": [B, H, L, D]}
+        for label, fn in (("reference_triton", ref_functional.sdpa_jvp), ("this_library", ours.sdpa_jvp)):
+            try:
+                leaves = [t[n].detach().requires_grad_(True) for n in ("q", "k", "v", "tq", "tk", "tv")]
+
+                def fwd():
+                    return torch.func.jvp(fn, tuple(leaves[:3]), tuple(leaves[3:]))
+
+                def time_it(f, reps):
+                    for _ in range(3):
+                        r = f()
+                    torch.cuda.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    for _ in range(reps):
+                        r = f()
+                    b.record()
+                    b.synchronize()
+                    return a.elapsed_time(b) / reps, r
+
+                reps = 20 if name == "config2" else 5
+                f_ms, (o, to) = time_it(fwd, reps)
+                both_ms, _ = time_it(lambda: torch.autograd.grad(list(fwd()), leaves, [t["g_o"], t["g_to"]]), reps)
+                row[label] = {"fwd_ms": f_ms, "fwd_bwd_ms": both_ms, "bwd_ms": both_ms - f_ms,
+                              "fwd_bwd_tflops": flops_per_step(B, H, L, D) / (both_ms * 1e-3) / 1e12}
+                if label == "reference_triton":
+                    ref_out = (o.detach().float(), to.detach().float())
+                else:
+                    row["max_abs_diff_vs_reference"] = {"o": float((o.detach().float() - ref_out[0]).abs().max()),
+                                                        "to": float((to.detach().float() - ref_out[1]).abs().max())}
+            except Exception as e:  # one attempt: the message is the record
+                row[label] = {"error": f"{type(e).__name__}: {e}"[:600]}
+                ref_out = None
+        out["rows"].append(row)
+    out["note"] = ("through the PyTorch entry point (autograd glue included on both sides), eager launches, both cotangents; "
+                   "the reference runs its tangent and primal backward as two calls, as does this library through autograd")
+    print(json.dumps(out))
+
+
 def _claim_stdout():
     """Libraries (NCCL among them) print banners on stdout; the contract is ONE JSON line there.  Point fd 1 at
     stderr for the rest of the process and hand back a file object on the real stdout for the final line."""
@@ -479,7 +544,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_triton"])
     ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS) + ["sweep5"])
     ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
     ap.add_argument("--primal-attention", default="sdpa", choices=["sdpa", "lib"],
@@ -488,6 +553,8 @@ def main():
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
     args = ap.parse_args()
+    if args.impl == "reference_triton":
+        return run_triton_comparator(args)
     if args.workload in TRAIN_CONFIGS:
         return main_train(args)
     if args.workload == "sweep5":

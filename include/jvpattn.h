@@ -120,6 +120,31 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
                         const float *cos, const float *sin, int batch, int len, int heads, int head_dim, int transpose,
                         void *stream);
 
+/* Caller-side helpers for the denoiser block around the attention (no counterpart among the reference's kernel wrappers;
+ * they replace chains of PyTorch pointwise ops that, under torch.func.jvp, run as separate primal and tangent kernels):
+ *   jvpattn_ln_modulate     h = LayerNorm(x) * (1 + scale) + shift      (semicat/net/duo.py:128-135, 159)
+ *   jvpattn_gated_residual  z = x + mask * (gate * y)                   (duo.py:157, 160; mask = dropout keep / (1 - p) or NULL)
+ * on (primal, tangent) pairs, with the VJPs of a cotangent on either output.  x, y, masks, outputs and gradients are
+ * contiguous (batch, len, channels) tensors, shift / scale / gate are (batch, channels) views whose rows are `*_stride`
+ * elements apart, gamma / beta are fp32 (channels); every other tensor has the one element type `dtype` (JVPATTN_BF16 or
+ * JVPATTN_FP32).  channels must be 256, 512, 768 or 1024 (else JVPATTN_EINVAL: the caller keeps its PyTorch ops).
+ * `which`: 0 forward (y; ln: also writes mean / rstd, fp32 (batch * len)), 1 forward of the tangent (ty from tx and the
+ * tangents of the modulation; NULL tangents are zeros), 2 VJP of a cotangent `g` on y, 3 (ln only) VJP of a cotangent on ty.
+ * The VJPs write the row-shaped gradients (ln: dx, dtx; gate: d1 = gradient of the gated branch, d2 = gradient of y through
+ * the tangent output) and ADD per-sample column sums into `sums` (fp32, (3, batch, channels) for ln: sum_s g n, sum_s g,
+ * sum_s g nd with n the normalised row and nd its tangent; (2, batch, channels) for gate: sum_s mask y g, sum_s mask ty g),
+ * which the caller zeroes beforehand and turns into the gradients of shift / scale / gate / gamma / beta
+ * (semicat_b200/dual_ops.py).  `exact` selects the VJP of the LayerNorm tangent with respect to x: 0 reproduces PyTorch,
+ * whose forward-mode formula for native_layer_norm treats the saved mean / rstd as constants when it is differentiated
+ * again; 1 includes their dependence on x. */
+int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
+                        const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
+                        float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int batch, int len,
+                        int channels, float eps, int exact, int dtype, void *stream);
+int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
+                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
+                           void *d2, float *sums, int batch, int len, int channels, int dtype, void *stream);
+
 /* Same backward for callers that have no way to allocate device memory (no counterpart in the reference,
  * whose wrappers allocate freely through torch).  Takes no workspace: the scratch lives in a fixed
  * 2 MiB array inside the library image, present on every GPU that loads the library until the process
@@ -149,7 +174,7 @@ uint64_t jvpattn_launch_count(void);
  * triton.testing.do_bench around whole calls, ryu_triton.py:958-1007).  Between _begin and _end every
  * launch is bracketed by CUDA events on its stream; _end synchronises the device and returns, per kernel
  * id in [0, JVPATTN_NUM_KERNELS), the summed device time in milliseconds and the launch count. */
-#define JVPATTN_NUM_KERNELS 8
+#define JVPATTN_NUM_KERNELS 9
 int jvpattn_profile_begin(void);
 int jvpattn_profile_end(double *total_ms, uint64_t *launches);
 const char *jvpattn_kernel_name(int id);

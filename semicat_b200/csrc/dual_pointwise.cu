@@ -1,0 +1,513 @@
+// Dual-number pointwise kernels for the denoiser block around the attention: every op takes a primal and a tangent and
+// returns both, and has hand-written VJPs for cotangents on either output.  Under torch.func.jvp the same algebra runs
+// as a dozen small kernels per op and per pass (primal and tangent separately), which is what bounds the training step
+// once the batch is sharded over several GPUs.
+//
+//   ln_modulate     h = LN(x) * (1 + scale) + shift        (semicat/net/duo.py:128-135, 159: LayerNorm + adaLN modulation)
+//   gated_residual  z = x + m * (g * y)                    (duo.py:157, 160: dropout(branch * gate) + skip; m = dropout keep
+//                                                           mask / (1 - p), all ones in evaluation)
+//
+// One warp owns one row of C channels (C = 256, 512, 768 or 1024; one element type, bf16 or fp32, for every tensor but
+// the fp32 LayerNorm weight and bias): 16-byte loads, fp32 arithmetic, warp-shuffle
+// row reductions.  Column sums that feed the gradients of per-sample or per-channel parameters are accumulated per CTA
+// in shared memory and added to fp32 [B, C] buffers with one atomic per column and CTA (a CTA stays inside one sample).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <type_traits>
+
+#include "jvpattn_common.cuh"
+
+namespace jvpattn {
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+
+template <typename T>
+__device__ __forceinline__ void load8(const T *p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float *p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4 *>(p)[0], b = reinterpret_cast<const float4 *>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16 *p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4 *>(p);
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T *p, const float (&f)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float *p, const float (&f)[8]) {
+  reinterpret_cast<float4 *>(p)[0] = make_float4(f[0], f[1], f[2], f[3]);
+  reinterpret_cast<float4 *>(p)[1] = make_float4(f[4], f[5], f[6], f[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16 *p, const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<uint4 *>(p) = u;
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// Channel index of element e of vector v of this lane: vectors of 8 channels, lanes interleaved (coalesced 16-byte loads).
+__device__ __forceinline__ int chan(int v, int lane) { return (v * 32 + lane) * 8; }
+
+struct LnArgs {
+  const void *x, *tx;            // [rows, C]
+  const float *gamma, *beta;     // [C] (beta may be null: no bias)
+  const void *shift, *scale;     // [B, C] rows `mod_stride` elements apart
+  const void *tshift, *tscale;   // tangents of shift / scale (null = zero)
+  int64_t mod_stride, tmod_stride;
+  float *mean, *rstd;            // [rows]
+  void *y;                       // output of the forward kernels
+  const void *g;                 // cotangent (backward kernels)
+  void *dx, *dtx;                // gradients with respect to x / tx
+  float *sums;                   // [3, B, C] fp32 column sums (zeroed by the caller)
+  int B, S, C;
+  float eps;
+  int exact;                     // backward of the tangent: 1 = full second-order terms, 0 = mean / rstd held constant
+};
+
+// ---- forward.  kTangent = false: y = (n gamma + beta)(1 + scale) + shift, saves mean / rstd.
+//               kTangent = true:  ty = nd gamma (1 + scale) + (n gamma + beta) tscale + tshift,  nd = rstd P_n(tx),
+//               where P_n(z) = z - mean(z) - n mean(n z)
+template <typename T, int NV, bool kTangent>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_fwd_kernel(LnArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + warp;
+  if (row >= (int64_t)a.B * a.S) return;
+  const int b = (int)(row / a.S);
+  constexpr int C = NV * 256;
+  const T *x = static_cast<const T *>(a.x) + row * C;
+  float xv[NV][8];
+  float s = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    load8<T>(x + chan(v, lane), xv[v]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += xv[v][i];
+  }
+  float mean, rstd;
+  if (!kTangent) {
+    mean = warp_sum(s) / C;
+    float q = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float d = xv[v][i] - mean;
+        q += d * d;
+      }
+    }
+    rstd = rsqrtf(warp_sum(q) / C + a.eps);
+    if (lane == 0) {
+      a.mean[row] = mean;
+      a.rstd[row] = rstd;
+    }
+  } else {
+    mean = a.mean[row];
+    rstd = a.rstd[row];
+  }
+  const T *sc = static_cast<const T *>(a.scale) + (int64_t)b * a.mod_stride;
+  T *y = static_cast<T *>(a.y) + row * C;
+  if (!kTangent) {
+    const T *sh = static_cast<const T *>(a.shift) + (int64_t)b * a.mod_stride;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float g[8], be[8], scv[8], shv[8], out[8];
+      load8<float>(a.gamma + c0, g);
+      if (a.beta) load8<float>(a.beta + c0, be);
+      load8<T>(sc + c0, scv);
+      load8<T>(sh + c0, shv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float ln = (xv[v][i] - mean) * rstd * g[i] + (a.beta ? be[i] : 0.f);
+        out[i] = ln * (1.f + scv[i]) + shv[i];
+      }
+      store8<T>(y + c0, out);
+    }
+  } else {
+    const T *tx = static_cast<const T *>(a.tx) + row * C;
+    float tv[NV][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      load8<T>(tx + chan(v, lane), tv[v]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s1 += tv[v][i];
+        s2 += (xv[v][i] - mean) * rstd * tv[v][i];
+      }
+    }
+    const float m1 = warp_sum(s1) / C, m2 = warp_sum(s2) / C;
+    const T *tsc = a.tscale ? static_cast<const T *>(a.tscale) + (int64_t)b * a.tmod_stride : nullptr;
+    const T *tsh = a.tshift ? static_cast<const T *>(a.tshift) + (int64_t)b * a.tmod_stride : nullptr;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float g[8], be[8], scv[8], tscv[8], tshv[8], out[8];
+      load8<float>(a.gamma + c0, g);
+      if (a.beta) load8<float>(a.beta + c0, be);
+      load8<T>(sc + c0, scv);
+      if (tsc) load8<T>(tsc + c0, tscv);
+      if (tsh) load8<T>(tsh + c0, tshv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float n = (xv[v][i] - mean) * rstd;
+        const float nd = rstd * (tv[v][i] - m1 - n * m2);
+        float o = nd * g[i] * (1.f + scv[i]);
+        if (tsc) o += (n * g[i] + (a.beta ? be[i] : 0.f)) * tscv[i];
+        if (tsh) o += tshv[i];
+        out[i] = o;
+      }
+      store8<T>(y + c0, out);
+    }
+  }
+}
+
+// Adds this warp's per-channel partial sums into the CTA's shared accumulators, then (whole CTA) into the global ones.
+template <int NQ, int NV>
+__device__ __forceinline__ void flush_column_sums(float *smem, const float (&part)[NQ][NV][8], int lane, float *const (&dst)[NQ]) {
+  constexpr int C = NV * 256;
+#pragma unroll
+  for (int q = 0; q < NQ; ++q)
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&smem[q * C + c0 + i], part[q][v][i]);
+    }
+  __syncthreads();
+  for (int q = 0; q < NQ; ++q)
+    for (int c = threadIdx.x; c < C; c += blockDim.x) atomicAdd(dst[q] + c, smem[q * C + c]);
+}
+
+// ---- backward of y.  u = G gamma (1 + scale);  dx = rstd P_n(u);  sums[0] += G n, sums[1] += G   (per sample)
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_kernel(LnArgs a, int rows_per_cta) {
+  extern __shared__ float smem_raw[];
+  constexpr int C = NV * 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) smem_raw[c] = 0.f;
+  __syncthreads();
+  const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
+  const int b = blockIdx.x / ctas_per_sample;
+  const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
+  const T *sc = static_cast<const T *>(a.scale) + (int64_t)b * a.mod_stride;
+  float part[2][NV][8] = {};
+  for (int r = warp; r < rows_per_cta && s0 + r < a.S; r += kWarpsPerCta) {
+    const int64_t row = (int64_t)b * a.S + s0 + r;
+    const T *x = static_cast<const T *>(a.x) + row * C;
+    const T *g = static_cast<const T *>(a.g) + row * C;
+    const float mean = a.mean[row], rstd = a.rstd[row];
+    float n[NV][8], u[NV][8];
+    float su = 0.f, sun = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float xv[8], gv[8], gam[8], scv[8];
+      load8<T>(x + c0, xv);
+      load8<T>(g + c0, gv);
+      load8<float>(a.gamma + c0, gam);
+      load8<T>(sc + c0, scv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        n[v][i] = (xv[i] - mean) * rstd;
+        u[v][i] = gv[i] * gam[i] * (1.f + scv[i]);
+        su += u[v][i];
+        sun += u[v][i] * n[v][i];
+        part[0][v][i] += gv[i] * n[v][i];
+        part[1][v][i] += gv[i];
+      }
+    }
+    const float mu_ = warp_sum(su) / C, mun = warp_sum(sun) / C;
+    T *dx = static_cast<T *>(a.dx) + row * C;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      float out[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = rstd * (u[v][i] - mu_ - n[v][i] * mun);
+      store8<T>(dx + chan(v, lane), out);
+    }
+  }
+  float *const dst[2] = {a.sums + (int64_t)b * C, a.sums + ((int64_t)a.B + b) * C};
+  flush_column_sums<2, NV>(smem_raw, part, lane, dst);
+}
+
+// ---- backward of ty.  u = G gamma (1 + scale), w = G gamma tscale, nd = rstd P_n(tx):
+//   dtx = rstd P_n(u)
+//   exact:        dx = rstd P_n(w + gn) - rstd n mean(u nd),   gn = -rstd (u mean(n tx) + tx mean(u n))
+//   mean / rstd held constant inside nd (what autograd does with the forward-mode formula of native_layer_norm, whose
+//   saved statistics are not differentiable outputs; the w term goes through the primal output and is differentiated
+//   in full):   dx = rstd P_n(w) - rstd^2 (u mean(n tx) + (tx - mean(tx)) mean(u n))
+//   sums[0] += G n, sums[1] += G, sums[2] += G nd   (per sample)
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_kernel(LnArgs a, int rows_per_cta) {
+  extern __shared__ float smem_raw[];
+  constexpr int C = NV * 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < 3 * C; c += blockDim.x) smem_raw[c] = 0.f;
+  __syncthreads();
+  const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
+  const int b = blockIdx.x / ctas_per_sample;
+  const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
+  const T *sc = static_cast<const T *>(a.scale) + (int64_t)b * a.mod_stride;
+  const T *tsc = a.tscale ? static_cast<const T *>(a.tscale) + (int64_t)b * a.tmod_stride : nullptr;
+  float part[3][NV][8] = {};
+  for (int r = warp; r < rows_per_cta && s0 + r < a.S; r += kWarpsPerCta) {
+    const int64_t row = (int64_t)b * a.S + s0 + r;
+    const T *x = static_cast<const T *>(a.x) + row * C;
+    const T *tx = static_cast<const T *>(a.tx) + row * C;
+    const T *g = static_cast<const T *>(a.g) + row * C;
+    const float mean = a.mean[row], rstd = a.rstd[row];
+    float n[NV][8], t[NV][8], gv[NV][8];
+    float st = 0.f, snt = 0.f, su = 0.f, sun = 0.f, sw = 0.f, swn = 0.f, sut = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float xv[8], gam[8], scv[8], tscv[8];
+      load8<T>(x + c0, xv);
+      load8<T>(tx + c0, t[v]);
+      load8<T>(g + c0, gv[v]);
+      load8<float>(a.gamma + c0, gam);
+      load8<T>(sc + c0, scv);
+      if (tsc) load8<T>(tsc + c0, tscv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        n[v][i] = (xv[i] - mean) * rstd;
+        const float gg = gv[v][i] * gam[i];
+        const float u = gg * (1.f + scv[i]), w = tsc ? gg * tscv[i] : 0.f;
+        st += t[v][i];
+        snt += n[v][i] * t[v][i];
+        su += u;
+        sun += u * n[v][i];
+        sw += w;
+        swn += w * n[v][i];
+        sut += u * t[v][i];
+      }
+    }
+    const float inv = 1.f / C;
+    const float m_t = warp_sum(st) * inv, m_nt = warp_sum(snt) * inv, m_u = warp_sum(su) * inv, m_un = warp_sum(sun) * inv;
+    const float m_w = warp_sum(sw) * inv, m_wn = warp_sum(swn) * inv, m_ut = warp_sum(sut) * inv;
+    // nd = rstd (t - m_t - n m_nt)   =>   mean(u nd) = rstd (m_ut - m_u m_t - m_un m_nt)
+    const float m_und = rstd * (m_ut - m_u * m_t - m_un * m_nt);
+    // gn = -rstd (u m_nt + t m_un)   =>   mean(gn) = -rstd (m_u m_nt + m_t m_un),  mean(gn n) = -2 rstd m_un m_nt
+    const float m_gn = -rstd * (m_u * m_nt + m_t * m_un), m_gnn = -2.f * rstd * m_un * m_nt;
+    T *dx = static_cast<T *>(a.dx) + row * C;
+    T *dtx = static_cast<T *>(a.dtx) + row * C;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float gam[8], scv[8], tscv[8], o1[8], o2[8];
+      load8<float>(a.gamma + c0, gam);  // (cache hits: the row loop above just read them)
+      load8<T>(sc + c0, scv);
+      if (tsc) load8<T>(tsc + c0, tscv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float gg = gv[v][i] * gam[i];
+        const float u = gg * (1.f + scv[i]), w = tsc ? gg * tscv[i] : 0.f;
+        const float nn = n[v][i], tt = t[v][i];
+        const float nd = rstd * (tt - m_t - nn * m_nt);
+        o2[i] = rstd * (u - m_u - nn * m_un);
+        if (a.exact) {
+          const float gn = -rstd * (u * m_nt + tt * m_un);
+          o1[i] = rstd * ((w + gn) - (m_w + m_gn) - nn * (m_wn + m_gnn)) - rstd * nn * m_und;
+        } else {
+          o1[i] = rstd * ((w - m_w - nn * m_wn) - rstd * (u * m_nt + (tt - m_t) * m_un));
+        }
+        part[0][v][i] += gv[v][i] * nn;
+        part[1][v][i] += gv[v][i];
+        part[2][v][i] += gv[v][i] * nd;
+      }
+      store8<T>(dx + c0, o1);
+      store8<T>(dtx + c0, o2);
+    }
+  }
+  float *const dst[3] = {a.sums + (int64_t)b * C, a.sums + ((int64_t)a.B + b) * C, a.sums + ((int64_t)2 * a.B + b) * C};
+  flush_column_sums<3, NV>(smem_raw, part, lane, dst);
+}
+
+// ---- gated residual.  z = x + m (g y)            tz = tx + m (g ty + tg y)
+// backward of z (cotangent G):   dx = G, dy = m g G, dg[b] += sum_s m y G
+// backward of tz (cotangent G):  dtx = G, dty = m g G, dtg[b] += sum_s m y G, dy = m tg G, dg[b] += sum_s m ty G
+struct GateArgs {
+  const void *x, *y, *ty;    // [rows, C]; x may be null in the tangent forward without a tangent on x
+  const void *gate, *tgate;  // [B, C] rows `gate_stride` / `tgate_stride` apart (tgate may be null)
+  const void *mask;          // [rows, C] in the branch dtype: keep mask / (1 - p); null = all ones
+  int64_t gate_stride, tgate_stride;
+  void *z;                   // output
+  const void *g;             // cotangent
+  void *d1, *d2;             // backward outputs (see the kernels)
+  float *sums;               // [2, B, C]
+  int B, S, C;
+};
+
+// mode 0: z = x + m g y.   mode 1: tz = tx + m (g ty + tg y)  (x = tx; either of tx / tg may be absent)
+template <typename T, int kMode>
+__global__ void __launch_bounds__(256) gated_residual_fwd_kernel(GateArgs a) {
+  using XT = T;
+  using YT = T;
+  using MT = T;
+  const int64_t total = (int64_t)a.B * a.S * a.C / 8;
+  for (int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i8 < total; i8 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = i8 * 8;
+    const int c0 = (int)(e % a.C);
+    const int b = (int)(e / ((int64_t)a.S * a.C));
+    float xv[8], yv[8], gv[8], mv[8], out[8];
+    if (a.x) load8<XT>(static_cast<const XT *>(a.x) + e, xv);
+    load8<MT>(static_cast<const MT *>(a.gate) + (int64_t)b * a.gate_stride + c0, gv);
+    if (a.mask) load8<YT>(static_cast<const YT *>(a.mask) + e, mv);
+    if (kMode == 0) {
+      load8<YT>(static_cast<const YT *>(a.y) + e, yv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) out[i] = (a.x ? xv[i] : 0.f) + (a.mask ? mv[i] : 1.f) * gv[i] * yv[i];
+    } else {
+      float tyv[8], tgv[8];
+      if (a.ty) load8<YT>(static_cast<const YT *>(a.ty) + e, tyv);
+      if (a.tgate) {
+        load8<YT>(static_cast<const YT *>(a.y) + e, yv);
+        load8<MT>(static_cast<const MT *>(a.tgate) + (int64_t)b * a.tgate_stride + c0, tgv);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float br = 0.f;
+        if (a.ty) br += gv[i] * tyv[i];
+        if (a.tgate) br += tgv[i] * yv[i];
+        out[i] = (a.x ? xv[i] : 0.f) + (a.mask ? mv[i] : 1.f) * br;
+      }
+    }
+    store8<XT>(static_cast<XT *>(a.z) + e, out);
+  }
+}
+
+// Backward: d1 = m gate G  (gradient of the branch that `gate` multiplies), sums[0][b] += sum_s m y G (gradient of
+// that gate); with `tgate`: d2 = m tgate G (gradient of y through the tangent output), and with `ty`:
+// sums[1][b] += sum_s m ty G (gradient of gate through the tangent output).  The skip gradient is G itself.
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(GateArgs a, int rows_per_cta) {
+  extern __shared__ float smem_raw[];
+  constexpr int C = NV * 256;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) smem_raw[c] = 0.f;
+  __syncthreads();
+  const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
+  const int b = blockIdx.x / ctas_per_sample;
+  const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
+  const T *gate = static_cast<const T *>(a.gate) + (int64_t)b * a.gate_stride;
+  const T *tgate = a.tgate ? static_cast<const T *>(a.tgate) + (int64_t)b * a.tgate_stride : nullptr;
+  float part[2][NV][8] = {};
+  for (int r = warp; r < rows_per_cta && s0 + r < a.S; r += kWarpsPerCta) {
+    const int64_t off = ((int64_t)b * a.S + s0 + r) * C;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const int c0 = chan(v, lane);
+      float gv[8], yv[8], tyv[8], mv[8], gt[8], tgt[8], o1[8], o2[8];
+      load8<T>(static_cast<const T *>(a.g) + off + c0, gv);
+      load8<T>(static_cast<const T *>(a.y) + off + c0, yv);
+      if (a.ty) load8<T>(static_cast<const T *>(a.ty) + off + c0, tyv);
+      if (a.mask) load8<T>(static_cast<const T *>(a.mask) + off + c0, mv);
+      load8<T>(gate + c0, gt);
+      if (tgate) load8<T>(tgate + c0, tgt);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float mg = (a.mask ? mv[i] : 1.f) * gv[i];
+        o1[i] = mg * gt[i];
+        part[0][v][i] += mg * yv[i];
+        if (tgate) o2[i] = mg * tgt[i];
+        if (a.ty) part[1][v][i] += mg * tyv[i];
+      }
+      store8<T>(static_cast<T *>(a.d1) + off + c0, o1);
+      if (tgate && a.d2) store8<T>(static_cast<T *>(a.d2) + off + c0, o2);
+    }
+  }
+  float *const dst[2] = {a.sums + (int64_t)b * C, a.sums + ((int64_t)a.B + b) * C};
+  flush_column_sums<2, NV>(smem_raw, part, lane, dst);
+}
+
+constexpr int kRowsPerCta = 16;
+
+// Calls f(T{}, integral_constant<NV>) for the element type (dtype code 0 = bf16, 2 = fp32) and C / 256 in 1..4.
+template <typename F>
+cudaError_t dispatch(int dtype, int C, F &&f) {
+  auto with_nv = [&](auto t) -> cudaError_t {
+    switch (C / 256) {
+      case 1: return f(t, std::integral_constant<int, 1>{});
+      case 2: return f(t, std::integral_constant<int, 2>{});
+      case 3: return f(t, std::integral_constant<int, 3>{});
+      case 4: return f(t, std::integral_constant<int, 4>{});
+      default: return cudaErrorInvalidValue;
+    }
+  };
+  if (dtype == JVPATTN_BF16) return with_nv(__nv_bfloat16{});
+  if (dtype == JVPATTN_FP32) return with_nv(float{});
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+bool dual_shape_ok(int B, int S, int C) { return B >= 0 && S >= 1 && C >= 256 && C <= 1024 && C % 256 == 0; }
+
+cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
+                        const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
+                        float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int B, int S, int C,
+                        float eps, int exact, int dtype, cudaStream_t stream) {
+  LnArgs a{x, tx, gamma, beta, shift, scale, tshift, tscale, mod_stride, tmod_stride, mean, rstd, out, g, dx, dtx, sums, B, S, C, eps, exact};
+  const int64_t rows = (int64_t)B * S;
+  if (rows == 0) return cudaSuccess;
+  LaunchScope scope(kIdDual, stream);
+  return dispatch(dtype, C, [&](auto t, auto nv) -> cudaError_t {
+    using T = decltype(t);
+    constexpr int NV = decltype(nv)::value;
+    if (which == 0 || which == 1) {
+      const unsigned grid = (unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta);
+      if (which == 0) ln_modulate_fwd_kernel<T, NV, false><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
+      else ln_modulate_fwd_kernel<T, NV, true><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
+    } else {
+      const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
+      if (which == 2) ln_modulate_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+      else ln_modulate_bwd_tangent_kernel<T, NV><<<grid, kWarpsPerCta * 32, 3 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+    }
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
+                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
+                           void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream) {
+  GateArgs a{x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, B, S, C};
+  const int64_t rows = (int64_t)B * S;
+  if (rows == 0) return cudaSuccess;
+  LaunchScope scope(kIdDual, stream);
+  return dispatch(dtype, C, [&](auto t, auto nv) -> cudaError_t {
+    using T = decltype(t);
+    constexpr int NV = decltype(nv)::value;
+    if (which == 0 || which == 1) {
+      const int64_t total = rows * C / 8;
+      const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+      if (which == 0) gated_residual_fwd_kernel<T, 0><<<grid, 256, 0, stream>>>(a);
+      else gated_residual_fwd_kernel<T, 1><<<grid, 256, 0, stream>>>(a);
+    } else {
+      const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
+      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+    }
+    return cudaGetLastError();
+  });
+}
+
+}  // namespace jvpattn

@@ -231,6 +231,41 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
                                static_cast<cudaStream_t>(stream)));
 }
 
+int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
+                        const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
+                        float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int batch, int len,
+                        int channels, float eps, int exact, int dtype, void *stream) {
+  if (which < 0 || which > 3 || !dual_shape_ok(batch, len, channels)) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * len == 0) return JVPATTN_OK;
+  if (!x || !gamma || !scale || !mean || !rstd) return JVPATTN_EINVAL;
+  if ((which == 0 && (!shift || !out)) || (which == 1 && (!tx || !out)) || (which >= 2 && (!g || !dx || !sums)) ||
+      (which == 3 && (!tx || !dtx)))
+    return JVPATTN_EINVAL;
+  if (mod_stride % 8 || tmod_stride % 8) return JVPATTN_EALIGN;
+  return note_cuda(ln_modulate(which, x, tx, gamma, beta, shift, scale, tshift, tscale, mod_stride, tmod_stride, mean, rstd, out, g,
+                               dx, dtx, sums, batch, len, channels, eps, exact, dtype, static_cast<cudaStream_t>(stream)));
+}
+
+int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
+                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
+                           void *d2, float *sums, int batch, int len, int channels, int dtype, void *stream) {
+  if (which < 0 || which > 2 || !dual_shape_ok(batch, len, channels)) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * len == 0) return JVPATTN_OK;
+  if (!gate) return JVPATTN_EINVAL;
+  if ((which == 0 && (!y || !z)) || (which == 1 && (!z || (!ty && !tgate) || (tgate && !y))) ||
+      (which == 2 && (!g || !y || !d1 || !sums)))
+    return JVPATTN_EINVAL;
+  if (gate_stride % 8 || tgate_stride % 8) return JVPATTN_EALIGN;
+  return note_cuda(gated_residual(which, x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, batch, len,
+                                  channels, dtype, static_cast<cudaStream_t>(stream)));
+}
+
 uint64_t jvpattn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char *jvpattn_last_cuda_error(void) { return t_cuda_error; }
@@ -293,6 +328,7 @@ const char *jvpattn_kernel_name(int id) {
     case kIdBwdQuerySimt: return "simt_bwd_q_kernel";
     case kIdBwdKeySimt: return "simt_bwd_kv_kernel";
     case kIdRotary: return "rotary_cast_kernel";
+    case kIdDual: return "dual_pointwise_kernels";
     default: return "?";
   }
 }

@@ -59,9 +59,19 @@ size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_l
 cudaError_t rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
                         const float *cosv, const float *sinv, int B, int S, int H, int D, int transpose, cudaStream_t stream);
 
+// dual_pointwise.cu: LayerNorm + modulation and gated residual on (primal, tangent) pairs, with their VJPs
+bool dual_shape_ok(int B, int S, int C);
+cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
+                        const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
+                        float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int B, int S, int C,
+                        float eps, int exact, int dtype, cudaStream_t stream);
+cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
+                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
+                           void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream);
+
 // Kernel identifiers used by the launch counter and the optional per-kernel event timing.
 enum KernelId {
-  kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kIdRotary, kNumKernelIds
+  kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kIdRotary, kIdDual, kNumKernelIds
 };
 
 // Brackets one kernel launch: counts it and, while profiling is on, records a CUDA event before and

@@ -1,0 +1,265 @@
+"""Fused (primal, tangent) pointwise ops for the denoiser block around the attention.
+
+Callers of ``safe_sdpa_jvp`` run the whole block under ``torch.func.jvp`` (semicat/models/semicat.py:153-157), where
+every pointwise op of semicat/net/duo.py:127-166 becomes several small kernels for the primal and several more for the
+tangent, and again for each of them in the backward.  Two ops cover most of that chain:
+
+* :func:`ln_modulate` - ``norm(x) * (1 + scale) + shift`` (duo.py:128-135 and :159),
+* :func:`gated_residual` - ``dropout(branch * gate) + skip`` (duo.py:157 and :160).
+
+Each is one kernel for the primal, one for the tangent (``jvp``), and one per cotangent in the backward, behind
+``torch.autograd.Function`` s that work under ``torch.func.jvp`` and are reverse-mode differentiable with respect to the
+primals AND the tangents.  CUDA only; shapes the kernels do not take (channels other than 256/512/768/1024, mixed
+dtypes) fall back to the equivalent PyTorch expression, so callers need no special cases.
+
+``ln_modulate`` differentiates the LayerNorm tangent like PyTorch does by default (``exact=False``): PyTorch's
+forward-mode formula for ``native_layer_norm`` reuses the saved mean and rstd, which are not differentiable outputs, so
+the reverse pass through the tangent treats them as constants.  ``exact=True`` includes their dependence on ``x``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+_CODES = {torch.bfloat16: 0, torch.float32: 2}
+
+
+def _usable(x: torch.Tensor, *others) -> bool:
+    if not x.is_cuda or x.dim() != 3 or x.dtype not in _CODES or x.shape[-1] not in (256, 512, 768, 1024):
+        return False
+    return all(o is None or (o.dtype == x.dtype and o.is_cuda) for o in others)
+
+
+def _rows(t: torch.Tensor | None, B: int, C: int):
+    """A (B, 1, C) or (B, C) modulation tensor as ((B, C) view with unit channel stride, row stride)."""
+    if t is None:
+        return None, 0
+    t = t.reshape(B, C) if t.dim() == 3 and t.is_contiguous() else (t[:, 0] if t.dim() == 3 else t)
+    if t.stride(-1) != 1 or t.stride(0) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t, t.stride(0)
+
+
+def _nz(t):
+    """A tangent as ``None`` when it is absent or a symbolic zero (torch.func.jvp hands inputs without a tangent an
+    efficient zero tensor)."""
+    if t is None or t._is_zerotensor():
+        return None
+    return t
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ln_launch(which, x, tx, gamma, beta, shift, scale, tshift, tscale, mean, rstd, out, g, dx, dtx, sums, eps, exact):
+    B, S, C = x.shape
+    sc, sc_stride = _rows(scale, B, C)
+    sh, sh_stride = _rows(shift, B, C)
+    tsc, tsc_stride = _rows(tscale, B, C)
+    tsh, tsh_stride = _rows(tshift, B, C)
+    if sh is not None and sh_stride != sc_stride:
+        sh = sh.contiguous()
+        sc = sc.contiguous()
+        sc_stride = sh_stride = C
+    if tsc is not None and tsh is not None and tsc_stride != tsh_stride:
+        tsc, tsh = tsc.contiguous(), tsh.contiguous()
+        tsc_stride = C
+    tstride = tsc_stride if tsc is not None else tsh_stride
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        rc = lib.jvpattn_ln_modulate(which, _ptr(x), _ptr(tx), _ptr(gamma), _ptr(beta), _ptr(sh), _ptr(sc), _ptr(tsh), _ptr(tsc),
+                                     sc_stride, tstride, _ptr(mean), _ptr(rstd), _ptr(out), _ptr(g), _ptr(dx), _ptr(dtx), _ptr(sums),
+                                     B, S, C, float(eps), int(exact), _CODES[x.dtype], _stream(x))
+    _lib.check(rc, "jvpattn_ln_modulate")
+
+
+class _LnModulateTangent(torch.autograd.Function):
+    """ty from (x, tx, scale, tshift, tscale) and the saved row statistics; backward = VJP of a cotangent on ty."""
+
+    @staticmethod
+    def forward(x, tx, gamma, beta, scale, tshift, tscale, mean, rstd, eps, exact):
+        tx_ = torch.zeros_like(x) if tx is None else tx.contiguous()
+        ty = torch.empty_like(x)
+        _ln_launch(1, x, tx_, gamma, beta, None, scale, tshift, tscale, mean, rstd, ty, None, None, None, None, eps, exact)
+        return ty
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, tx, gamma, beta, scale, tshift, tscale, mean, rstd, eps, exact = inputs
+        ctx.save_for_backward(x, tx, gamma, beta, scale, tshift, tscale, mean, rstd)
+        ctx.eps, ctx.exact = eps, exact
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        x, tx, gamma, beta, scale, tshift, tscale, mean, rstd = ctx.saved_tensors
+        B, S, C = x.shape
+        tx_ = torch.zeros_like(x) if tx is None else tx.contiguous()
+        dx, dtx = torch.empty_like(x), torch.empty_like(x)
+        sums = torch.zeros(3, B, C, dtype=torch.float32, device=x.device)
+        _ln_launch(3, x, tx_, gamma, None, None, scale, None, tscale, mean, rstd, None, g.contiguous(), dx, dtx, sums, ctx.eps, ctx.exact)
+        gn, g1, gnd = sums[0], sums[1], sums[2]
+        like = lambda v, ref: None if ref is None else v.to(ref.dtype).reshape(ref.shape)
+        sc32 = scale.reshape(B, C).float()
+        d_tshift = like(g1, tshift)
+        d_tscale = like(gamma * gn + (beta * g1 if beta is not None else 0.0), tscale)
+        d_scale = like(gamma * gnd, scale)
+        d_gamma = (gnd * (1.0 + sc32)).sum(0)
+        d_beta = None
+        if tscale is not None:
+            ts32 = tscale.reshape(B, C).float()
+            d_gamma = d_gamma + (gn * ts32).sum(0)
+            d_beta = (g1 * ts32).sum(0) if beta is not None else None
+        elif beta is not None:
+            d_beta = torch.zeros_like(beta)
+        return dx, (dtx if tx is not None else None), d_gamma, d_beta, d_scale, d_tshift, d_tscale, None, None, None, None
+
+
+class _LnModulate(torch.autograd.Function):
+    @staticmethod
+    def forward(x, gamma, beta, shift, scale, eps, exact):
+        B, S, C = x.shape
+        y = torch.empty_like(x)
+        mean = torch.empty(B * S, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        _ln_launch(0, x, None, gamma, beta, shift, scale, None, None, mean, rstd, y, None, None, None, None, eps, exact)
+        return y, mean, rstd
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, gamma, beta, shift, scale, eps, exact = inputs
+        _, mean, rstd = output
+        ctx.mark_non_differentiable(mean, rstd)
+        ctx.save_for_backward(x, gamma, beta, shift, scale, mean, rstd)
+        ctx.save_for_forward(x, gamma, beta, scale, mean, rstd)
+        ctx.eps, ctx.exact = eps, exact
+
+    @staticmethod
+    def jvp(ctx, tx, tgamma, tbeta, tshift, tscale, *_):
+        # tgamma / tbeta are ignored: the LayerNorm weight and bias are parameters and carry no tangent where this is
+        # used (torch.func.jvp hands over materialised zeros for them, which cannot be told from a real tangent)
+        x, gamma, beta, scale, mean, rstd = ctx.saved_for_forward
+        ty = _LnModulateTangent.apply(x, _nz(tx), gamma, beta, scale, _nz(tshift), _nz(tscale), mean, rstd, ctx.eps, ctx.exact)
+        return ty, None, None
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g, _gm, _gr):
+        x, gamma, beta, shift, scale, mean, rstd = ctx.saved_tensors
+        B, S, C = x.shape
+        dx = torch.empty_like(x)
+        sums = torch.zeros(2, B, C, dtype=torch.float32, device=x.device)
+        _ln_launch(2, x, None, gamma, None, None, scale, None, None, mean, rstd, None, g.contiguous(), dx, None, sums, ctx.eps, ctx.exact)
+        gn, g1 = sums[0], sums[1]
+        sc1 = 1.0 + scale.reshape(B, C).float()
+        d_shift = g1.to(shift.dtype).reshape(shift.shape)
+        d_scale = (gamma * gn + (beta * g1 if beta is not None else 0.0)).to(scale.dtype).reshape(scale.shape)
+        d_gamma = (gn * sc1).sum(0)
+        d_beta = (g1 * sc1).sum(0) if beta is not None else None
+        return dx, d_gamma, d_beta, d_shift, d_scale, None, None
+
+
+def ln_modulate(x: torch.Tensor, norm: torch.nn.LayerNorm, shift: torch.Tensor, scale: torch.Tensor, exact: bool = False) -> torch.Tensor:
+    """``norm(x) * (1 + scale) + shift`` for ``x`` (B, S, C) and per-sample ``shift`` / ``scale`` ((B, 1, C) or (B, C)).
+    The result has the dtype of ``x`` (under autocast the reference computes it in fp32 and the next linear layer rounds
+    it to bf16: the same values)."""
+    if norm.weight is None or not _usable(x, shift, scale) or tuple(norm.normalized_shape) != (x.shape[-1],):
+        return norm(x) * (1.0 + scale) + shift
+    beta = norm.bias.float() if norm.bias is not None else None
+    y, _, _ = _LnModulate.apply(x.contiguous(), norm.weight.float(), beta, shift, scale, norm.eps, exact)
+    return y
+
+
+def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums):
+    B, S, C = y.shape
+    gt, gt_stride = _rows(gate, B, C)
+    tg, tg_stride = _rows(tgate, B, C)
+    lib = _lib.load()
+    with torch.cuda.device(y.device):
+        rc = lib.jvpattn_gated_residual(which, _ptr(x), _ptr(y), _ptr(ty), _ptr(gt), _ptr(tg), _ptr(mask), gt_stride, tg_stride,
+                                        _ptr(z), _ptr(g), _ptr(d1), _ptr(d2), _ptr(sums), B, S, C, _CODES[y.dtype], _stream(y))
+    _lib.check(rc, "jvpattn_gated_residual")
+
+
+class _GatedResidualTangent(torch.autograd.Function):
+    """tz = tx + mask * (gate * ty + tgate * y); any of tx, ty, tgate may be absent (zero)."""
+
+    @staticmethod
+    def forward(tx, y, ty, gate, tgate, mask):
+        if ty is None and tgate is None:
+            return tx.clone() if tx is not None else torch.zeros_like(y)
+        tz = torch.empty_like(y)
+        c = lambda t: None if t is None else t.contiguous()
+        _gate_launch(1, c(tx), y, c(ty), gate, tgate, mask, tz, None, None, None, None)
+        return tz
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        tx, y, ty, gate, tgate, mask = inputs
+        ctx.save_for_backward(y, ty, gate, tgate, mask)
+        ctx.has_tx = tx is not None
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        y, ty, gate, tgate, mask = ctx.saved_tensors
+        B, S, C = y.shape
+        g = g.contiguous()
+        d_tx = g if ctx.has_tx else None
+        if ty is None and tgate is None:
+            return d_tx, None, None, None, None, None
+        d_ty = torch.empty_like(y)
+        d_y = torch.empty_like(y) if tgate is not None else None
+        sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
+        _gate_launch(2, None, y, None if ty is None else ty.contiguous(), gate, tgate, mask, None, g, d_ty, d_y, sums)
+        d_tgate = sums[0].to(tgate.dtype).reshape(tgate.shape) if tgate is not None else None
+        d_gate = sums[1].to(gate.dtype).reshape(gate.shape) if ty is not None else None
+        return d_tx, d_y, (d_ty if ty is not None else None), d_gate, d_tgate, None
+
+
+class _GatedResidual(torch.autograd.Function):
+    @staticmethod
+    def forward(x, y, gate, mask):
+        z = torch.empty_like(y)
+        _gate_launch(0, x, y, None, gate, None, mask, z, None, None, None, None)
+        return z
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, y, gate, mask = inputs
+        ctx.save_for_backward(y, gate, mask)
+        ctx.save_for_forward(y, gate, mask)
+
+    @staticmethod
+    def jvp(ctx, tx, ty, tgate, _tmask):
+        y, gate, mask = ctx.saved_for_forward
+        return _GatedResidualTangent.apply(_nz(tx), y, _nz(ty), gate, _nz(tgate), mask)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        y, gate, mask = ctx.saved_tensors
+        B, S, C = y.shape
+        g = g.contiguous()
+        d_y = torch.empty_like(y)
+        sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
+        _gate_launch(2, None, y, None, gate, None, mask, None, g, d_y, None, sums)
+        return g, d_y, sums[0].to(gate.dtype).reshape(gate.shape), None
+
+
+def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor, p: float = 0.0, training: bool = False) -> torch.Tensor:
+    """``dropout(branch * gate, p) + skip`` with ``gate`` (B, 1, C) or (B, C).  The dropout keep mask (scaled by
+    1 / (1 - p)) is drawn once and shared by primal, tangent and both backward passes."""
+    if not _usable(branch, skip, gate) or skip.shape != branch.shape:
+        return F.dropout(branch * gate, p, training) + skip
+    mask = None
+    if training and p > 0.0:
+        mask = torch.empty_like(branch).bernoulli_(1.0 - p).div_(1.0 - p)
+    return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)

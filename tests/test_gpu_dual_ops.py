@@ -1,0 +1,150 @@
+"""GPU parity of the fused (primal, tangent) pointwise ops (``semicat_b200.dual_ops``) against the PyTorch expressions they
+replace (semicat/net/duo.py:128-135, 157-160), evaluated in fp32 under ``torch.func.jvp`` and differentiated in reverse
+mode with cotangents on both the primal and the tangent output."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from semicat_b200 import _lib, dual_ops
+
+
+def _manual_ln(x, w, b, eps):
+    mu = x.mean(-1, keepdim=True)
+    xc = x - mu
+    return xc * ((xc * xc).mean(-1, keepdim=True) + eps).rsqrt() * w + b
+
+
+def _run(fn, primals, tangents, cots):
+    leaves = [p.detach().clone().requires_grad_(True) for p in primals]
+    tleaves = [None if t is None else t.detach().clone().requires_grad_(True) for t in tangents]
+    idx = [i for i, t in enumerate(tleaves) if t is not None]
+
+    def call(*dual):
+        args = list(leaves)
+        for i, d in zip(idx, dual):
+            args[i] = d
+        return fn(*args)
+
+    y, ty = torch.func.jvp(call, tuple(leaves[i] for i in idx), tuple(tleaves[i] for i in idx))
+    wrt = leaves + [t for t in tleaves if t is not None]
+    grads = torch.autograd.grad([y, ty], wrt, [cots[0].to(y.dtype), cots[1].to(ty.dtype)], allow_unused=True)
+    return y, ty, grads
+
+
+def _close(a, b, what, rtol, atol):
+    if a is None or b is None:
+        assert a is None and b is None or (b is None and float(a.abs().max()) == 0) or (a is None and float(b.abs().max()) == 0), what
+        return
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    assert bool((err <= tol).all()), f"{what}: max err {err.max().item():.3e} (ref max {b.abs().max().item():.3e})"
+
+
+def _ln_inputs(B, S, C, dtype, seed=0, tx=True):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    x, t = r(B, S, C).to(dtype), (r(B, S, C).to(dtype) if tx else None)
+    mod = (r(B, 1, 6 * C) * 0.5).to(dtype)  # chunks of one projection, as in the denoiser: strided (B, 1, C) views
+    tmod = (r(B, 1, 6 * C) * 0.5).to(dtype)
+    sh, sc = mod[..., :C], mod[..., C:2 * C]
+    tsh, tsc = tmod[..., :C], tmod[..., C:2 * C]
+    norm = torch.nn.LayerNorm(C).cuda()
+    with torch.no_grad():
+        norm.weight.copy_(1.0 + 0.3 * r(C))
+        norm.bias.copy_(0.2 * r(C))
+    cots = (r(B, S, C), r(B, S, C))
+    return x, t, sh, sc, tsh, tsc, norm, cots
+
+
+@pytest.mark.parametrize("exact", [False, True])
+@pytest.mark.parametrize("shape", [(3, 40, 768), (2, 17, 256), (1, 128, 1024)])
+def test_ln_modulate_fp32_matches_pytorch(shape, exact):
+    B, S, C = shape
+    x, t, sh, sc, tsh, tsc, norm, cots = _ln_inputs(B, S, C, torch.float32)
+    w, b = norm.weight, norm.bias
+    if exact:
+        ref_fn = lambda x_, sh_, sc_, w_, b_: _manual_ln(x_, w_, b_, norm.eps) * (1.0 + sc_) + sh_
+    else:  # PyTorch's own LayerNorm: its forward-mode formula holds mean / rstd constant when differentiated again
+        ref_fn = lambda x_, sh_, sc_, w_, b_: F.layer_norm(x_, (C,), w_, b_, norm.eps) * (1.0 + sc_) + sh_
+
+    def fused(x_, sh_, sc_, w_, b_):
+        y, _, _ = dual_ops._LnModulate.apply(x_, w_, b_, sh_, sc_, norm.eps, exact)
+        return y
+
+    before = _lib.launch_count()
+    got = _run(fused, (x, sh, sc, w, b), (t, tsh, tsc, None, None), cots)
+    assert _lib.launch_count() - before == 4  # primal, tangent, and one backward per cotangent
+    want = _run(ref_fn, (x, sh, sc, w, b), (t, tsh, tsc, None, None), cots)
+    _close(got[0], want[0], "y", 1e-4, 1e-4)
+    _close(got[1], want[1], "ty", 1e-4, 1e-4)
+    for name, a, r in zip(("dx", "dshift", "dscale", "dgamma", "dbeta", "dtx", "dtshift", "dtscale"), got[2], want[2]):
+        _close(a, r, f"{name} (exact={exact})", 2e-3, 2e-3 * float(r.abs().max()))
+
+
+def test_ln_modulate_bf16_and_missing_tangent_on_x():
+    """bf16 tensors as under autocast; the first block of the denoiser sees a tangent on the modulation only."""
+    B, S, C = 4, 64, 768
+    for tx in (True, False):
+        x, t, sh, sc, tsh, tsc, norm, cots = _ln_inputs(B, S, C, torch.bfloat16, seed=3, tx=tx)
+        fused = lambda x_, sh_, sc_: dual_ops.ln_modulate(x_, norm, sh_, sc_)
+        ref_fn = lambda x_, sh_, sc_: F.layer_norm(x_.float(), (C,), norm.weight, norm.bias, norm.eps) * (1.0 + sc_.float()) + sh_.float()
+        got = _run(fused, (x, sh, sc), (t, tsh, tsc), cots)
+        want = _run(ref_fn, (x, sh, sc), (t, tsh, tsc), cots)
+        assert got[0].dtype == torch.bfloat16
+        _close(got[0], want[0], "y", 2e-2, 2e-2)
+        _close(got[1], want[1], "ty", 2e-2, 4e-2)
+        for name, a, r in zip(("dx", "dshift", "dscale", "dtx", "dtshift", "dtscale") if tx else ("dx", "dshift", "dscale", "dtshift", "dtscale"),
+                              got[2], want[2]):
+            _close(a, r, f"{name} (tx={tx})", 3e-2, 3e-2 * float(r.float().abs().max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_residual_matches_pytorch(dtype):
+    B, S, C = 3, 50, 768
+    g = torch.Generator(device="cuda").manual_seed(5)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g).to(dtype)
+    x, y, tx, ty = r(B, S, C), r(B, S, C), r(B, S, C), r(B, S, C)
+    gates, tgates = r(B, 1, 6 * C), r(B, 1, 6 * C)
+    gate, tgate = gates[..., 2 * C:3 * C], tgates[..., 2 * C:3 * C]
+    cots = (torch.randn(B, S, C, device="cuda", generator=g), torch.randn(B, S, C, device="cuda", generator=g))
+    fused = lambda x_, y_, g_: dual_ops.gated_residual(x_, y_, g_, p=0.1, training=False)
+    ref_fn = lambda x_, y_, g_: y_.float() * g_.float() + x_.float()
+    before = _lib.launch_count()
+    got = _run(fused, (x, y, gate), (tx, ty, tgate), cots)
+    assert _lib.launch_count() - before == 4
+    want = _run(ref_fn, (x, y, gate), (tx, ty, tgate), cots)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    _close(got[0], want[0], "z", tol, tol)
+    _close(got[1], want[1], "tz", tol, 2 * tol)
+    for name, a, rr in zip(("dx", "dy", "dgate", "dtx", "dty", "dtgate"), got[2], want[2]):
+        _close(a, rr, name, tol, tol * float(rr.float().abs().max()) + 1e-6)
+
+
+def test_gated_residual_dropout_uses_one_mask_for_primal_and_tangent():
+    B, S, C = 2, 64, 512
+    g = torch.Generator(device="cuda").manual_seed(9)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    x, y, tx, ty, gate = r(B, S, C), r(B, S, C), r(B, S, C), r(B, S, C), r(B, 1, C)
+    z, tz = torch.func.jvp(lambda x_, y_: dual_ops.gated_residual(x_, y_, gate, p=0.25, training=True), (x, y), (tx, ty))
+    kept = (z - x) != 0
+    frac = kept.float().mean().item()
+    assert 0.70 < frac < 0.80, frac
+    assert torch.allclose((z - x)[kept], (y * gate / 0.75)[kept], rtol=1e-5, atol=1e-6)
+    assert torch.equal((tz - tx) != 0, kept)  # same mask
+    assert torch.allclose((tz - tx)[kept], (ty * gate / 0.75)[kept], rtol=1e-5, atol=1e-6)
+
+
+def test_unsupported_shapes_fall_back_to_pytorch():
+    x = torch.randn(2, 8, 96, device="cuda")
+    norm = torch.nn.LayerNorm(96).cuda()
+    sh, sc = torch.randn(2, 1, 96, device="cuda"), torch.randn(2, 1, 96, device="cuda")
+    before = _lib.launch_count()
+    y = dual_ops.ln_modulate(x, norm, sh, sc)
+    assert _lib.launch_count() == before
+    assert torch.allclose(y, norm(x) * (1 + sc) + sh)
+    z = dual_ops.gated_residual(x, x, sc)
+    assert torch.allclose(z, x * sc + x)
