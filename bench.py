@@ -307,7 +307,7 @@ def count_step_flops(body, attn_flops):
 
 
 def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp", use_graph=True,
-              primal_attention="sdpa"):
+              primal_attention="lib"):
     """Flow-map training steps of the DiT (semicat_b200/train_step.py) on uniform random tokens: global batch
     sharded over the ranks, forward-mode JVP through every attention layer for the first `sd_prop` of each
     shard, AdamW, one flat gradient all-reduce per step.  Every step copies its token ids from pinned host memory
@@ -415,11 +415,14 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     peak_gb = torch.cuda.max_memory_allocated() / 1e9
     graph = None
     nbytes = flat.nbytes()
+    from semicat_b200 import _lib
+    status = _lib.device_status()  # non-zero: a bounded wait inside one of the library's kernels ran out
     del net, opt, flat
     torch.cuda.empty_cache()
     return {"ms_per_step": ms, "ms_per_step_median": med, "tokens_per_step": tc["global_batch"] * tc["length"],
             "loss": last_loss, "peak_mem_gb": peak_gb, "launch": mode, "allreduce_ms": ar_ms, "allreduce_bytes": nbytes,
-            "flops_per_step": step_flops, "steps": steps, "warmup": max(warmup, 3), "primal_attention": primal_attention}
+            "flops_per_step": step_flops, "steps": steps, "warmup": max(warmup, 3), "primal_attention": primal_attention,
+            "device_status": status, "ms_per_step_max": max(per_step), "ms_per_step_min": min(per_step)}
 
 
 def train_block(r, world, pk, label):
@@ -429,7 +432,8 @@ def train_block(r, world, pk, label):
     return {"workload": label, "scaling": "strong", "ms_per_step": r["ms_per_step"], "ms_per_step_median": r["ms_per_step_median"],
             "tokens_per_s": tps, "tokens_per_s_median": r["tokens_per_step"] / (r["ms_per_step_median"] * 1e-3),
             "steps": r["steps"], "warmup": r["warmup"], "loss": r["loss"], "launch": r["launch"], "peak_mem_gb": r["peak_mem_gb"],
-            "primal_attention": r["primal_attention"],
+            "primal_attention": r["primal_attention"], "device_status": r["device_status"],
+            "ms_per_step_min": r["ms_per_step_min"], "ms_per_step_max": r["ms_per_step_max"],
             "allreduce_ms": r["allreduce_ms"], "allreduce_bytes": r["allreduce_bytes"],
             "flops_per_step": r["flops_per_step"], "flops_source": "torch.utils.flop_counter over one eager step + algorithmic "
             "FLOPs of the library's attention calls", "tflops": tf, "frac_of_bf16_peak": tf / (world * pk["bf16_tflops"])}
@@ -547,7 +551,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_triton"])
     ap.add_argument("--workload", default="config2", choices=list(WORKLOADS) + list(TRAIN_CONFIGS) + ["sweep5"])
     ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
-    ap.add_argument("--primal-attention", default="sdpa", choices=["sdpa", "lib"],
+    ap.add_argument("--primal-attention", default="lib", choices=["sdpa", "lib"],
                     help="attention of the passes without tangents in the training workloads: torch SDPA or this library")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",

@@ -65,7 +65,7 @@ struct BwdSmem {
   // flight holds a scoreboard slot that the tensor-memory reads of the score algebra also wait on, which exposed
   // the memory latency once per item even with nothing depending on the load.
   alignas(16) float xstat[kXBuf][4][kRows];
-  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done, r2_free, done, vdone;
+  uint64_t x_full[kXBuf], x_empty[kXBuf], acc_free, y_full[kStages], y_empty[kStages], s1_full, s2_full, c1_done, c2_done[2], r2_free, done, vdone;
   uint32_t tmem_base;
 };
 
@@ -211,7 +211,8 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
     mbar_init(&s.s1_full, 1);
     mbar_init(&s.s2_full, 1);
     mbar_init(&s.c1_done, kComputeThreads);
-    mbar_init(&s.c2_done, kComputeThreads);
+    mbar_init(&s.c2_done[0], kComputeThreads);
+    mbar_init(&s.c2_done[1], kComputeThreads);
     mbar_init(&s.r2_free, kComputeThreads);
     mbar_init(&s.done, 1);
     mbar_init(&s.vdone, 1);
@@ -248,7 +249,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         decode(it_, b, h, x0);
         const int xb = n_ % kXBuf;
         if (!mbar_wait_for(a.wait_cycles, &s.x_empty[xb], ((n_ / kXBuf) & 1) ^ 1)) {
-          atomicExch(a.status, 209u);
+          atomicCAS(a.status, 0u, 209u);
           return false;
         }
         mbar_expect_tx(&s.x_full[xb], __popc(a.xmask) * kRows * D * 2 + (kKV ? 0 : (has_t ? 4 : 3) * kRows * 4));
@@ -297,7 +298,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         for (int j = 0; j < ntiles; ++j, ++g) {
           const int st = g % kStages;
           if (!mbar_wait_for(a.wait_cycles, &s.y_empty[st], ((g / kStages) & 1) ^ 1)) {
-            atomicExch(a.status, 201u);
+            atomicCAS(a.status, 0u, 201u);
             ok = false;
             break;
           }
@@ -425,12 +426,12 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         bool ok = it < items;
         if (warp == 1) {
           if (ok && !mbar_wait_for(a.wait_cycles, &s.x_full[0], 0)) {
-            atomicExch(a.status, 202u);
+            atomicCAS(a.status, 0u, 202u);
             ok = false;
           }
           if (ok) {
             if (!scores1(0, 0, false)) {
-              atomicExch(a.status, 203u);
+              atomicCAS(a.status, 0u, 203u);
               ok = false;
             } else {
               scores2(0, 0, ntiles == 1);
@@ -445,19 +446,19 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
             }
             if (it2 >= items) break;
             if (!mbar_wait_for(a.wait_cycles, &s.c1_done, g & 1)) {  // (S | Sd) of tile g has been read
-              atomicExch(a.status, 204u);
+              atomicCAS(a.status, 0u, 204u);
               break;
             }
             if (j2 == 0 && !mbar_wait_for(a.wait_cycles, &s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
-              atomicExch(a.status, 202u);
+              atomicCAS(a.status, 0u, 202u);
               break;
             }
             if (!scores1(g + 1, n2 % kXBuf, false)) {
-              atomicExch(a.status, 203u);
+              atomicCAS(a.status, 0u, 203u);
               break;
             }
             if (!mbar_wait_for(a.wait_cycles, &s.r2_free, g & 1)) {  // (A | C) of tile g has been read
-              atomicExch(a.status, 207u);
+              atomicCAS(a.status, 0u, 215u);
               break;
             }
             tc_fence_after();
@@ -468,12 +469,17 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
           const bool acc_merge = kMerge && has_t;
           for (; ok; ) {
             const int st = g % kStages;
-            if (!mbar_wait_for(a.wait_cycles, &s.c2_done, g & 1)) {  // W1 / W2 of tile g are in place
-              atomicExch(a.status, 207u);
+            // Two barriers, by tile parity.  Nothing that this thread issues gates the second half of the score algebra,
+            // so the compute warps can complete two tiles (g and g + 1) while this thread is still held up behind the
+            // other issuer's MMAs, and a parity wait on a single barrier would then take the incomplete phase g + 2
+            // for phase g and never return.  Tile g + 2 cannot complete before outK(g) (its streamed stage is reloaded
+            // only then), so with one barrier per parity the wait is unambiguous.
+            if (!mbar_wait_for(a.wait_cycles, &s.c2_done[g & 1], (g >> 1) & 1)) {  // W1 / W2 of tile g are in place
+              atomicCAS(a.status, 0u, 216u);
               break;
             }
             if (j == 0 && !mbar_wait_for(a.wait_cycles, &s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
-              atomicExch(a.status, 210u);
+              atomicCAS(a.status, 0u, 210u);
               break;
             }
             tc_fence_after();
@@ -514,12 +520,12 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       int it = blockIdx.x, j = 0, n = 0, g = 0;
       bool ok = it < items;
       if (ok && !mbar_wait_for(a.wait_cycles, &s.x_full[0], 0)) {
-        atomicExch(a.status, 202u);
+        atomicCAS(a.status, 0u, 202u);
         ok = false;
       }
       if (ok) {
         if (!scores1(0, 0, ntiles == 1)) {
-          atomicExch(a.status, 203u);
+          atomicCAS(a.status, 0u, 203u);
           ok = false;
         } else {
           scores2(0, 0, ntiles == 1);
@@ -538,11 +544,11 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         const bool has_next = it2 < items;
         if (j == 0) init0 = init1 = initv = initvd = false;
         if (!mbar_wait_for(a.wait_cycles, &s.c1_done, g & 1)) {
-          atomicExch(a.status, 204u);
+          atomicCAS(a.status, 0u, 204u);
           break;
         }
         if (j == 0 && !mbar_wait_for(a.wait_cycles, &s.acc_free, (n & 1) ^ 1)) {  // previous item's accumulators have been read out
-          atomicExch(a.status, 210u);
+          atomicCAS(a.status, 0u, 210u);
           break;
         }
         tc_fence_after();
@@ -580,17 +586,17 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         if (kEarlyV && j == ntiles - 1) tc_commit(&s.vdone);  // dV / dVd of this item are final
         if (has_next) {
           if (j2 == 0 && !mbar_wait_for(a.wait_cycles, &s.x_full[n2 % kXBuf], (n2 / kXBuf) & 1)) {
-            atomicExch(a.status, 202u);
+            atomicCAS(a.status, 0u, 202u);
             break;
           }
           if (!scores1(g + 1, n2 % kXBuf, j2 == ntiles - 1)) {
-            atomicExch(a.status, 203u);
+            atomicCAS(a.status, 0u, 203u);
             break;
           }
         }
         if (kDoK) {
-          if (!mbar_wait_for(a.wait_cycles, &s.c2_done, g & 1)) {
-            atomicExch(a.status, 207u);
+          if (!mbar_wait_for(a.wait_cycles, &s.c2_done[0], g & 1)) {
+            atomicCAS(a.status, 0u, 207u);
             break;
           }
           tc_fence_after();
@@ -660,7 +666,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
     if (!kKV) {
       const int xb_ = n % kXBuf;
       if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.x_full[xb_], (n / kXBuf) & 1))) {
-        atomicExch(a.status, 211u);
+        atomicCAS(a.status, 0u, 211u);
         ok = false;
       }
       if (ok && x0 + row < a.Lx)
@@ -676,7 +682,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       }
       // a warp whose wait ran out keeps walking the loops without touching TMEM so that the barrier above still matches
       if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s1_full, g & 1))) {
-        atomicExch(a.status, 205u);
+        atomicCAS(a.status, 0u, 205u);
         ok = false;
       }
       if (!ok) continue;
@@ -744,7 +750,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       if (!kDoK) continue;
       // ---- second half: W1 = scale P (A - delta), W2 = scale P ((A - delta) N + C - dsum)
       if (!__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s2_full, g & 1))) {
-        atomicExch(a.status, 208u);
+        atomicCAS(a.status, 0u, 208u);
         ok = false;
         continue;
       }
@@ -788,7 +794,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&s.c2_done);
+      mbar_arrive(&s.c2_done[kSplit ? (g & 1) : 0]);
     }
     // ---- epilogue of the item: accumulators -> 16-bit outputs, each thread 1/kParts of the channels of its row
     {
@@ -841,7 +847,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
       };
       if (kEarlyV) {
         if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.vdone, n & 1))) {
-          atomicExch(a.status, 214u);
+          atomicCAS(a.status, 0u, 214u);
           ok = false;
         }
         tc_fence_after();
@@ -851,7 +857,7 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
         }
       }
       if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.done, n & 1))) {
-        atomicExch(a.status, 206u);
+        atomicCAS(a.status, 0u, 206u);
         ok = false;
       }
       tc_fence_after();

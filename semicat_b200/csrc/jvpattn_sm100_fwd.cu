@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
       for (int j = kStages; j < ntiles; ++j) {  // the first kStages tiles were requested before the set-up barrier
         const int st = j % kStages;
         if (!mbar_wait_for(a.wait_cycles, &s.kv_empty[st], ((j / kStages) & 1) ^ 1)) {
-          atomicExch(a.status, 101u);
+          atomicCAS(a.status, 0u, 101u);
           break;
         }
         mbar_expect_tx(&s.kv_full[st], (kHasT ? 4 : 2) * kBN * D * 2);
@@ -140,11 +140,11 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
       const uint32_t base16 = smem_u32(&s) >> 4;
       constexpr uint32_t kQTile = kBM * 128, kKvTile = kBN * 128;  // bytes of one 64-channel box
       bool ok = mbar_wait_for(a.wait_cycles, &s.q_full, 0);
-      if (!ok) atomicExch(a.status, 102u);
+      if (!ok) atomicCAS(a.status, 0u, 102u);
       for (int j = 0; ok && j < ntiles; ++j) {
         const int st = j % kStages;
         if (!mbar_wait_for(a.wait_cycles, &s.kv_full[st], (j / kStages) & 1)) {
-          atomicExch(a.status, 103u);
+          atomicCAS(a.status, 0u, 103u);
           break;
         }
         tc_fence_after();
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
         }
         tc_commit(&s.s_full);
         if (!mbar_wait_for(a.wait_cycles, &s.p_full, j & 1)) {
-          atomicExch(a.status, 104u);
+          atomicCAS(a.status, 0u, 104u);
           break;
         }
         tc_fence_after();
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     for (int j = 0; j < ntiles; ++j) {
       // tcgen05.ld / st are warp-collective: keep every decision that guards them warp-uniform
       if (!__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.s_full, j & 1))) {
-        atomicExch(a.status, 105u);
+        atomicCAS(a.status, 0u, 105u);
         ok = false;
         break;
       }
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, D == 64 ? 2 : 1) sm100_fwd_kernel(co
     }
     // ---- epilogue: O = acc / l ; Od = Od'/l - (mu/l) O ; statistics
     if (ok && !__all_sync(0xffffffffu, mbar_wait_for(a.wait_cycles, &s.o_done, (ntiles - 1) & 1))) {
-      atomicExch(a.status, 106u);
+      atomicCAS(a.status, 0u, 106u);
       ok = false;
     }
     tc_fence_after();

@@ -24,6 +24,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .dual_ops import gated_residual, ln_modulate
 from .functional import safe_sdpa_jvp
 from .rotary import apply_rotary_cast
 
@@ -88,7 +89,10 @@ class Block(nn.Module):
     def forward(self, x, cos, sin, c, attention):
         B, S, _ = x.shape
         sh1, sc1, g1, sh2, sc2, g2 = self.ada(c)[:, None].chunk(6, dim=2)
-        h = self.norm1(x) * (1.0 + sc1) + sh1
+        # On the GPU the pointwise chain around the attention runs as fused (primal, tangent) kernels (dual_ops); the
+        # plain-formula path ("math") keeps the PyTorch expressions and serves as the independent check.
+        fused = x.is_cuda and attention != "math"
+        h = ln_modulate(x, self.norm1, sh1, sc1) if fused else self.norm1(x) * (1.0 + sc1) + sh1
         q, k, v = self.attn_qkv(h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
         if x.is_cuda and attention != "math":
             # one kernel per tensor (and per tangent) instead of the fp32 pointwise chain plus the casts to bf16
@@ -107,6 +111,9 @@ class Block(nn.Module):
             a = (w @ vh).transpose(1, 2).to(x.dtype)
         else:
             a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2).to(q.dtype)).transpose(1, 2)
+        if fused:
+            x = gated_residual(x, self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)), g1, self.drop.p, self.training)
+            return gated_residual(x, self.mlp(ln_modulate(x, self.norm2, sh2, sc2)), g2, self.drop.p, self.training)
         x = self.drop(self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)) * g1) + x
         return self.drop(self.mlp(self.norm2(x) * (1.0 + sc2) + sh2) * g2) + x
 
@@ -237,26 +244,26 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     B = x1.shape[0]
     split = int(sd_prop * B)
     dev_type = x1.device.type
-    ac = lambda: torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None)
     x0 = noise["x0"]
-    # VFM step on the tail of the batch
-    vf_loss = None
-    if split < B:
-        t = noise["t_vfm"][split:]
-        xt = interpolate(x0[split:], x1[split:], t.view(-1, 1, 1))
-        with ac():
+    # One autocast region for the whole objective: the bf16 copies of the weights that autocast makes are cached per
+    # region, so the cross-entropy pass, the forward-mode pass and the no-grad target pass share one set of casts.
+    with torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
+        # VFM step on the tail of the batch
+        vf_loss = None
+        if split < B:
+            t = noise["t_vfm"][split:]
+            xt = interpolate(x0[split:], x1[split:], t.view(-1, 1, 1))
             pred = net(xt, t, t, attention=primal_attention)
-        # Same value as the reference's F.cross_entropy(pred.transpose(-1, 1), x1) (semicat.py:107-111): mean over all
-        # tokens.  With the classes innermost the log-softmax over the 30522-entry vocabulary runs as a row softmax;
-        # in the transposed (B, V, L) layout it is a strided "spatial" softmax that took a third of the whole step.
-        vf_loss = F.cross_entropy(pred.float().reshape(-1, pred.shape[-1]), x1[split:].reshape(-1), label_smoothing=label_smoothing)
-    if split == 0:
-        return vf_loss, None
-    # self-distillation ("lag") step on the head of the batch: d/dt of the flow map by forward-mode AD
-    t = noise["t_sd"][:split]
-    s = noise["u_sd"][:split] * t
-    xs = interpolate(x0[:split], x1[:split], s.view(-1, 1, 1))
-    with ac():
+            # Same value as the reference's F.cross_entropy(pred.transpose(-1, 1), x1) (semicat.py:107-111): mean over all
+            # tokens.  With the classes innermost the log-softmax over the 30522-entry vocabulary runs as a row softmax;
+            # in the transposed (B, V, L) layout it is a strided "spatial" softmax that took a third of the whole step.
+            vf_loss = F.cross_entropy(pred.float().reshape(-1, pred.shape[-1]), x1[split:].reshape(-1), label_smoothing=label_smoothing)
+        if split == 0:
+            return vf_loss, None
+        # self-distillation ("lag") step on the head of the batch: d/dt of the flow map by forward-mode AD
+        t = noise["t_sd"][:split]
+        s = noise["u_sd"][:split] * t
+        xs = interpolate(x0[:split], x1[:split], s.view(-1, 1, 1))
         xst, dv = torch.func.jvp(lambda _t: flow_map(net, xs, s, _t, jvp_attention), (t,), (torch.ones_like(t),))
         xst = xst.detach()
         with torch.no_grad():
