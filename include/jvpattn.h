@@ -145,6 +145,19 @@ int jvpattn_gated_residual(int which, const void *x, const void *y, const void *
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
                            void *d2, float *sums, int batch, int len, int channels, int dtype, void *stream);
 
+/* Vocabulary-side head of the flow-map step (no counterpart among the reference's kernel wrappers; it replaces the softmax
+ * over the vocabulary and the pointwise chain around it in semicat/models/semicat.py:210-229 and its forward-mode tangent,
+ * :153-157):   xst = x + dt (softmax(logits) - x),   dv = ddt (p - x) + dt p o (tlogits - sum(p tlogits)).
+ * logits / tlogits: (batch, rows_per_sample, vocab) of `dtype` (JVPATTN_BF16 or JVPATTN_FP32) with rows `ld_*` elements
+ * apart; x, out, g: fp32 contiguous; dt, ddt: fp32 (batch); lse: fp32 (batch * rows_per_sample), written by which = 0
+ * and read by the others.  which: 0 forward (out = xst), 1 forward of the tangent (out = dv), 2 VJP of a cotangent g on
+ * xst (writes dlogits), 3 VJP of a cotangent g on dv (writes dlogits and dtlogits); gradients are contiguous, in `dtype`.
+ * x, dt and ddt are data of the step (no gradient is formed for them).  A row pair must fit 200 KB of shared memory
+ * (vocab <= 51200 for bf16, 25600 for fp32), else JVPATTN_EINVAL. */
+int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, int64_t ld_logits, int64_t ld_tlogits, const float *x,
+                          const float *dt, const float *ddt, float *lse, float *out, const float *g, void *dlogits,
+                          void *dtlogits, int batch, int rows_per_sample, int vocab, int dtype, void *stream);
+
 /* Same backward for callers that have no way to allocate device memory (no counterpart in the reference,
  * whose wrappers allocate freely through torch).  Takes no workspace: the scratch lives in a fixed
  * 2 MiB array inside the library image, present on every GPU that loads the library until the process

@@ -16,7 +16,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG_DIR, "csrc")
 LIB_PATH = os.path.join(_PKG_DIR, "libjvpattn.so")
 SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu",
-           "sm100_tensormap.cu", "rotary.cu", "dual_pointwise.cu"]
+           "sm100_tensormap.cu", "rotary.cu", "dual_pointwise.cu", "vocab_head.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
@@ -30,7 +30,7 @@ EXPORTS = (
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
     "jvpattn_bwd_static", "jvpattn_rotary_cast", "jvpattn_stream_check", "jvpattn_debug_set",
-    "jvpattn_ln_modulate", "jvpattn_gated_residual",
+    "jvpattn_ln_modulate", "jvpattn_gated_residual", "jvpattn_flow_map_head",
 )
 DEBUG_WAIT_CYCLES, DEBUG_STALL_NEXT_FWD = 0, 1
 STATIC_SCRATCH_ROWS = 262144
@@ -129,6 +129,8 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_ln_modulate.restype = ctypes.c_int
         lib.jvpattn_gated_residual.argtypes = [I] + [V] * 6 + [I64, I64] + [V] * 5 + [I, I, I, I, V]
         lib.jvpattn_gated_residual.restype = ctypes.c_int
+        lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
+        lib.jvpattn_flow_map_head.restype = ctypes.c_int
         lib.jvpattn_stream_check.argtypes = [ctypes.c_void_p]
         lib.jvpattn_stream_check.restype = ctypes.c_int
         lib.jvpattn_debug_set.argtypes = [ctypes.c_int, ctypes.c_longlong]

@@ -266,6 +266,23 @@ int jvpattn_gated_residual(int which, const void *x, const void *y, const void *
                                   channels, dtype, static_cast<cudaStream_t>(stream)));
 }
 
+int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, int64_t ld_logits, int64_t ld_tlogits, const float *x,
+                          const float *dt, const float *ddt, float *lse, float *out, const float *g, void *dlogits,
+                          void *dtlogits, int batch, int rows_per_sample, int vocab, int dtype, void *stream) {
+  if (which < 0 || which > 3 || batch < 0 || rows_per_sample < 0 || vocab < 1) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  if ((size_t)((vocab + 7) & ~7) * (dtype == JVPATTN_BF16 ? 4 : 8) > 200 * 1024) return JVPATTN_EINVAL;  // the row pair must fit shared memory
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * rows_per_sample == 0) return JVPATTN_OK;
+  if (!logits || !dt || !lse) return JVPATTN_EINVAL;
+  if ((which == 0 && (!x || !out)) || (which == 1 && (!x || !out || !tlogits || !ddt)) || (which == 2 && (!g || !dlogits)) ||
+      (which == 3 && (!g || !dlogits || !dtlogits || !tlogits || !ddt)))
+    return JVPATTN_EINVAL;
+  return note_cuda(vocab_head(which, logits, tlogits, ld_logits, ld_tlogits, x, dt, ddt, lse, out, g, dlogits, dtlogits, batch,
+                              rows_per_sample, vocab, dtype, static_cast<cudaStream_t>(stream)));
+}
+
 uint64_t jvpattn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char *jvpattn_last_cuda_error(void) { return t_cuda_error; }

@@ -69,6 +69,11 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
                            void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream);
 
+// vocab_head.cu: flow-map head over the vocabulary axis on (primal, tangent) pairs, with its VJPs
+cudaError_t vocab_head(int which, const void *l, const void *tl, int64_t ldl, int64_t ldt, const float *x, const float *dt,
+                       const float *ddt, float *lse, float *out, const float *g, void *dl, void *dtl, int batch,
+                       int rows_per_sample, int V, int dtype, cudaStream_t stream);
+
 // Kernel identifiers used by the launch counter and the optional per-kernel event timing.
 enum KernelId {
   kIdFwdTc = 0, kIdRowDots, kIdBwdQueryTc, kIdBwdKeyTc, kIdFwdSimt, kIdBwdQuerySimt, kIdBwdKeySimt, kIdRotary, kIdDual, kNumKernelIds

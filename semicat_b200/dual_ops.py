@@ -263,3 +263,97 @@ def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor,
     if training and p > 0.0:
         mask = torch.empty_like(branch).bernoulli_(1.0 - p).div_(1.0 - p)
     return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)
+
+
+# ----------------------------------------------------------------------------------------------- vocabulary-side head
+def _rows3(t: torch.Tensor):
+    """A (B, L, V) tensor with unit innermost stride and uniformly spaced rows, and that row spacing."""
+    if t.stride(-1) != 1 or t.stride(0) != t.shape[1] * t.stride(1):
+        t = t.contiguous()
+    return t, t.stride(1)
+
+
+def _head_launch(which, logits, tlogits, x, dt, ddt, lse, out, g, dl, dtl):
+    B, L, V = logits.shape
+    logits, ld = _rows3(logits)
+    ldt = 0
+    if tlogits is not None:
+        tlogits, ldt = _rows3(tlogits)
+    lib = _lib.load()
+    with torch.cuda.device(logits.device):
+        rc = lib.jvpattn_flow_map_head(which, _ptr(logits), _ptr(tlogits), ld, ldt, _ptr(x), _ptr(dt), _ptr(ddt), _ptr(lse), _ptr(out),
+                                       _ptr(g), _ptr(dl), _ptr(dtl), B, L, V, _CODES[logits.dtype], _stream(logits))
+    _lib.check(rc, "jvpattn_flow_map_head")
+
+
+class _FlowHeadTangent(torch.autograd.Function):
+    """dv = ddt (p - x) + dt p o (tlogits - sum(p tlogits)); backward = VJP of a cotangent on dv w.r.t. both logits."""
+
+    @staticmethod
+    def forward(logits, tlogits, x, dt, ddt, lse):
+        dv = torch.empty(logits.shape, dtype=torch.float32, device=logits.device)
+        _head_launch(1, logits, tlogits, x, dt, ddt, lse, dv, None, None, None)
+        return dv
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(*inputs)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, h):
+        logits, tlogits, x, dt, ddt, lse = ctx.saved_tensors
+        dl = torch.empty(logits.shape, dtype=logits.dtype, device=logits.device)
+        dtl = torch.empty_like(dl)
+        _head_launch(3, logits, tlogits, None, dt, ddt, lse, None, h.float().contiguous(), dl, dtl)
+        return dl, dtl, None, None, None, None
+
+
+class _FlowHead(torch.autograd.Function):
+    @staticmethod
+    def forward(logits, x, dt):
+        B, L, V = logits.shape
+        xst = torch.empty((B, L, V), dtype=torch.float32, device=logits.device)
+        lse = torch.empty(B * L, dtype=torch.float32, device=logits.device)
+        _head_launch(0, logits, None, x, dt, None, lse, xst, None, None, None)
+        return xst, lse
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        logits, x, dt = inputs
+        _, lse = output
+        ctx.mark_non_differentiable(lse)
+        ctx.save_for_backward(logits, dt, lse)
+        ctx.save_for_forward(logits, x, dt, lse)
+
+    @staticmethod
+    def jvp(ctx, tlogits, _tx, tdt):
+        # x is data of the step (the interpolated input) and carries no tangent
+        logits, x, dt, lse = ctx.saved_for_forward
+        if tdt is None:
+            tdt = torch.zeros_like(dt)
+        if tlogits is None:
+            tlogits = torch.zeros_like(logits)
+        return _FlowHeadTangent.apply(logits, tlogits, x, dt, tdt.float().contiguous(), lse), None
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g, _glse):
+        logits, dt, lse = ctx.saved_tensors
+        dl = torch.empty(logits.shape, dtype=logits.dtype, device=logits.device)
+        _head_launch(2, logits, None, None, dt, None, lse, None, g.float().contiguous(), dl, None)
+        return dl, None, None
+
+
+def flow_map_head(logits: torch.Tensor, x: torch.Tensor, dt: torch.Tensor) -> torch.Tensor:
+    """``x + dt[:, None, None] * (softmax(logits, -1) - x)`` in fp32: the flow map of semicat/models/semicat.py:210-229 from
+    the denoiser's logits (B, L, V), the interpolated input ``x`` (fp32, treated as data: no tangent, no gradient) and the
+    per-sample step ``dt`` (B,) (data as well; its forward-mode tangent is used, no gradient is formed for it).  Works
+    under ``torch.func.jvp`` (the tangent is the flow map's derivative) and is reverse-mode differentiable with respect
+    to the logits and their tangent."""
+    usable = (logits.is_cuda and logits.dim() == 3 and logits.dtype in _CODES and x.dtype == torch.float32 and x.is_contiguous()
+              and x.shape == logits.shape and logits.shape[-1] * (4 if logits.dtype == torch.bfloat16 else 8) <= 200 * 1024 - 64)
+    if not usable:
+        return x + dt.view(-1, 1, 1) * (logits.softmax(dim=-1) - x)
+    xst, _ = _FlowHead.apply(logits, x, dt.float().contiguous())
+    return xst

@@ -24,7 +24,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .dual_ops import gated_residual, ln_modulate
+from .dual_ops import flow_map_head, gated_residual, ln_modulate
 from .functional import safe_sdpa_jvp
 from .rotary import apply_rotary_cast
 
@@ -222,7 +222,10 @@ def interpolate(x0, x1, t):
 
 def flow_map(net, x, s, t, attention):
     dt = (t - s) / (1.0 - s + 1e-8)
-    diff = net(x, s, t, attention=attention).softmax(dim=-1) - x
+    logits = net(x, s, t, attention=attention)
+    if logits.is_cuda and attention != "math":  # one fused pass over the vocabulary axis (primal, tangent and their VJPs)
+        return flow_map_head(logits, x, dt)
+    diff = logits.softmax(dim=-1) - x
     return x + dt.view(-1, 1, 1) * diff
 
 

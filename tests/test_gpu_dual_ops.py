@@ -148,3 +148,40 @@ def test_unsupported_shapes_fall_back_to_pytorch():
     assert torch.allclose(y, norm(x) * (1 + sc) + sh)
     z = dual_ops.gated_residual(x, x, sc)
     assert torch.allclose(z, x * sc + x)
+
+
+@pytest.mark.parametrize("dtype,V,pad", [(torch.float32, 27, 0), (torch.bfloat16, 30522, 6), (torch.float32, 1000, 0)])
+def test_flow_map_head_matches_pytorch(dtype, V, pad):
+    """xst = x + dt (softmax(l) - x) and its derivative in t, with cotangents on both, against the PyTorch expression in
+    fp32; the 30522-wide case reads the logits as a view of a padded (…, 30528) projection output, as the denoiser does."""
+    B, L = 3, 5
+    g = torch.Generator(device="cuda").manual_seed(2)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    lfull, tlfull = (2.0 * r(B, L, V + pad)).to(dtype), r(B, L, V + pad).to(dtype)
+    l, tl = lfull[..., :V], tlfull[..., :V]
+    x = r(B, L, V)
+    t = torch.rand(B, device="cuda", generator=g) * 0.8 + 0.1
+    s = torch.rand(B, device="cuda", generator=g) * t
+    cots = (r(B, L, V), r(B, L, V))
+
+    def run(fn):
+        ll, tll = l.detach().clone().requires_grad_(True), tl.detach().clone().requires_grad_(True)
+        tt = t.clone()
+
+        def f(l_, t_):
+            dt = (t_ - s) / (1.0 - s + 1e-8)
+            return fn(l_, x, dt)
+
+        xst, dv = torch.func.jvp(f, (ll, tt), (tll, torch.ones_like(tt)))
+        grads = torch.autograd.grad([xst, dv], [ll, tll], list(cots))
+        return xst, dv, grads
+
+    before = _lib.launch_count()
+    got = run(dual_ops.flow_map_head)
+    assert _lib.launch_count() - before == 4
+    want = run(lambda l_, x_, dt: x_ + dt.view(-1, 1, 1) * (l_.float().softmax(dim=-1) - x_))
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    _close(got[0], want[0], "xst", tol, 1e-5)
+    _close(got[1], want[1], "dv", tol, 1e-4 if dtype == torch.float32 else 1e-3)
+    for name, a, b in zip(("dlogits", "dtlogits"), got[2], want[2]):
+        _close(a, b, name, tol, (1e-5 if dtype == torch.float32 else 2e-2) * float(b.float().abs().max()))
