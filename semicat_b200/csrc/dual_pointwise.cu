@@ -10,7 +10,8 @@
 // One warp owns one row of C channels (C = 256, 512, 768 or 1024; one element type, bf16 or fp32, for every tensor but
 // the fp32 LayerNorm weight and bias): 16-byte loads, fp32 arithmetic, warp-shuffle
 // row reductions.  Column sums that feed the gradients of per-sample or per-channel parameters are accumulated per CTA
-// in shared memory and added to fp32 [B, C] buffers with one atomic per column and CTA (a CTA stays inside one sample).
+// (registers, then one shared-memory slice per warp) and added to fp32 [B, C] buffers with one atomic per column and
+// CTA (a CTA stays inside one sample).
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -181,21 +182,30 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_fwd_kernel(LnAr
   }
 }
 
-// Adds this warp's per-channel partial sums into the CTA's shared accumulators, then (whole CTA) into the global ones.
+// Column sums of a CTA: every warp parks its per-channel partial sums in its own slice of shared memory (plain stores),
+// then the CTA adds the slices and issues one global atomic per column.  `smem` holds kWarpsPerCta * NQ * C floats.
 template <int NQ, int NV>
 __device__ __forceinline__ void flush_column_sums(float *smem, const float (&part)[NQ][NV][8], int lane, float *const (&dst)[NQ]) {
   constexpr int C = NV * 256;
+  const int warp = threadIdx.x >> 5;
+  float *mine = smem + (size_t)warp * NQ * C;
 #pragma unroll
   for (int q = 0; q < NQ; ++q)
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-      const int c0 = chan(v, lane);
+      float f[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&smem[q * C + c0 + i], part[q][v][i]);
+      for (int i = 0; i < 8; ++i) f[i] = part[q][v][i];
+      store8<float>(mine + q * C + chan(v, lane), f);
     }
   __syncthreads();
   for (int q = 0; q < NQ; ++q)
-    for (int c = threadIdx.x; c < C; c += blockDim.x) atomicAdd(dst[q] + c, smem[q * C + c]);
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarpsPerCta; ++w) t += smem[((size_t)w * NQ + q) * C + c];
+      atomicAdd(dst[q] + c, t);
+    }
 }
 
 // ---- backward of y.  u = G gamma (1 + scale);  dx = rstd P_n(u);  sums[0] += G n, sums[1] += G   (per sample)
@@ -204,8 +214,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_kernel(LnAr
   extern __shared__ float smem_raw[];
   constexpr int C = NV * 256;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) smem_raw[c] = 0.f;
-  __syncthreads();
   const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
   const int b = blockIdx.x / ctas_per_sample;
   const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
@@ -262,8 +270,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_ker
   extern __shared__ float smem_raw[];
   constexpr int C = NV * 256;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = threadIdx.x; c < 3 * C; c += blockDim.x) smem_raw[c] = 0.f;
-  __syncthreads();
   const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
   const int b = blockIdx.x / ctas_per_sample;
   const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
@@ -404,8 +410,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(G
   extern __shared__ float smem_raw[];
   constexpr int C = NV * 256;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int c = threadIdx.x; c < 2 * C; c += blockDim.x) smem_raw[c] = 0.f;
-  __syncthreads();
   const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
   const int b = blockIdx.x / ctas_per_sample;
   const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
@@ -480,8 +484,14 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
       else ln_modulate_fwd_kernel<T, NV, true><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
     } else {
       const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
-      if (which == 2) ln_modulate_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
-      else ln_modulate_bwd_tangent_kernel<T, NV><<<grid, kWarpsPerCta * 32, 3 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+      if (which == 2) {
+        ln_modulate_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+      } else {
+        auto k = ln_modulate_bwd_tangent_kernel<T, NV>;
+        constexpr int smem = kWarpsPerCta * 3 * NV * 256 * 4;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        k<<<grid, kWarpsPerCta * 32, smem, stream>>>(a, kRowsPerCta);
+      }
     }
     return cudaGetLastError();
   });
@@ -504,7 +514,7 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
       else gated_residual_fwd_kernel<T, 1><<<grid, 256, 0, stream>>>(a);
     } else {
       const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
-      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
     }
     return cudaGetLastError();
   });

@@ -19,7 +19,7 @@
 namespace jvpattn {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 512;
 
 template <typename T> __device__ __forceinline__ float ldf(const T *p);
 template <> __device__ __forceinline__ float ldf<float>(const float *p) { return *p; }
@@ -42,13 +42,13 @@ __device__ __forceinline__ void block_reduce(float (&v)[NQ], float *scratch) {
   __syncthreads();  // scratch may still be read from an earlier reduction
   if (lane == 0)
 #pragma unroll
-    for (int q = 0; q < NQ; ++q) scratch[q * 8 + warp] = v[q];
+    for (int q = 0; q < NQ; ++q) scratch[q * 16 + warp] = v[q];
   __syncthreads();
 #pragma unroll
   for (int q = 0; q < NQ; ++q) {
-    float r = scratch[q * 8];
+    float r = scratch[q * 16];
 #pragma unroll
-    for (int w = 1; w < kThreads / 32; ++w) r = kMax ? fmaxf(r, scratch[q * 8 + w]) : r + scratch[q * 8 + w];
+    for (int w = 1; w < kThreads / 32; ++w) r = kMax ? fmaxf(r, scratch[q * 16 + w]) : r + scratch[q * 16 + w];
     v[q] = r;
   }
 }
@@ -69,7 +69,7 @@ struct HeadArgs {
 template <typename T, int kWhich>
 __global__ void __launch_bounds__(kThreads) vocab_head_kernel(HeadArgs a) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ float scratch[4 * 8];
+  __shared__ float scratch[4 * 16];
   T *sl = reinterpret_cast<T *>(smem_raw);
   T *stl = sl + ((a.V + 7) & ~7);
   const int64_t row = blockIdx.x;
@@ -78,9 +78,20 @@ __global__ void __launch_bounds__(kThreads) vocab_head_kernel(HeadArgs a) {
   const T *l = static_cast<const T *>(a.l) + row * a.ldl;
   constexpr bool kNeedT = kWhich == 1 || kWhich == 3;
   const T *tl = kNeedT ? static_cast<const T *>(a.tl) + row * a.ldt : nullptr;
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    sl[i] = l[i];
-    if (kNeedT) stl[i] = tl[i];
+  // stage the row(s): 16-byte copies where the row start is 16-byte aligned (a padded projection output is), element
+  // copies for the ragged tail and for unaligned rows
+  {
+    constexpr int kPer = 16 / (int)sizeof(T);
+    const bool al = (reinterpret_cast<uintptr_t>(l) % 16 == 0) && (!kNeedT || reinterpret_cast<uintptr_t>(tl) % 16 == 0);
+    const int nvec = al ? V / kPer : 0;
+    for (int i = threadIdx.x; i < nvec; i += kThreads) {
+      reinterpret_cast<uint4 *>(sl)[i] = reinterpret_cast<const uint4 *>(l)[i];
+      if (kNeedT) reinterpret_cast<uint4 *>(stl)[i] = reinterpret_cast<const uint4 *>(tl)[i];
+    }
+    for (int i = nvec * kPer + threadIdx.x; i < V; i += kThreads) {
+      sl[i] = l[i];
+      if (kNeedT) stl[i] = tl[i];
+    }
   }
   __syncthreads();
   const float dt = a.dt[b];
@@ -154,7 +165,7 @@ cudaError_t vocab_head(int which, const void *l, const void *tl, int64_t ldl, in
   const int64_t rows = (int64_t)batch * rows_per_sample;
   if (rows == 0) return cudaSuccess;
   const size_t esz = dtype == JVPATTN_BF16 ? 2 : 4;
-  const size_t smem = 2 * (size_t)((V + 7) & ~7) * esz;
+  const size_t smem = ((which == 1 || which == 3) ? 2 : 1) * (size_t)((V + 7) & ~7) * esz;  // logits (+ their tangent)
   if (smem > 200 * 1024) return cudaErrorInvalidValue;
   LaunchScope scope(kIdDual, stream);
   auto launch = [&](auto t) -> cudaError_t {
