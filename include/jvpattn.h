@@ -193,7 +193,7 @@ int jvpattn_profile_end(double *total_ms, uint64_t *launches);
 const char *jvpattn_kernel_name(int id);
 
 /* Synchronises the current device and returns the device-side status word: 0 if no bounded wait has
- * run out since the last call, else a code identifying the wait that gave up (101..107 forward, 201..214
+ * run out since the last call, else a code identifying the wait that gave up (101..107 forward, 201..216
  * backward).  Clears the word.  Every wait inside the kernels is bounded (about two seconds): a kernel whose
  * wait runs out stops computing, leaves through its normal teardown and leaves its outputs unwritten or partial;
  * the context stays usable. */
