@@ -158,6 +158,34 @@ int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, in
                           const float *dt, const float *ddt, float *lse, float *out, const float *g, void *dlogits,
                           void *dtlogits, int batch, int rows_per_sample, int vocab, int dtype, void *stream);
 
+/* GELU (tanh form) of the block's MLP on a (primal, tangent) pair (semicat/net/duo.py:118-123), n contiguous elements of
+ * `dtype` (n a multiple of 8, 16-byte aligned pointers).  mode 0: out = gelu(h).  mode 1: out = gelu'(h) * v - the
+ * forward-mode tangent (v = tangent of h) and the VJP of either output with respect to its own input (v = cotangent).
+ * mode 2: out = gelu'(h) * v and out2 = gelu''(h) * w * v - the VJP of the tangent output (v = its cotangent,
+ * w = the tangent of h) with respect to the tangent (out) and to h (out2). */
+int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
+                      void *stream);
+
+/* Vocabulary-side ends of the flow-map training step with nothing of size (rows, vocab) materialised in fp32
+ * (no counterpart among the reference's kernel wrappers; replaces the PyTorch passes of semicat/models/semicat.py:70-85,
+ * 89-110, 112-167 with sd_type "lag", 210-229).  rows = batch * rows_per_sample; row r belongs to sample r / rows_per_sample.
+ *   x0      fp32 noise, row pitch ldx elements;   ids  int64 (rows) token ids;   s, t  fp32 (batch) times
+ *   logits, tlogits, target_logits   `dtype` (JVPATTN_BF16 or JVPATTN_FP32), row pitch ld (multiple of 8, >= vocab rounded
+ *            up to 8; the columns from vocab on are ignored), 16-byte aligned
+ *   out, out2   `dtype`, row pitch ldo (same rule); columns from vocab on are written as zeros
+ *   lse (rows), stats (rows, 4), loss (rows)   fp32;   g   fp32 scalar in device memory: cotangent of the MEAN of `loss`
+ * op 0  out = (1 - t) x0 + t onehot(ids)                                            (the interpolated input, :70-85)
+ * op 1  out = xs + dt (softmax(logits) - xs), xs = (1 - s) x0 + s onehot(ids), dt = (t - s) / (1 - s + 1e-8); writes lse
+ * op 2  loss = cross-entropy(logits, ids) with label smoothing eps; writes lse       (:107-111)
+ * op 3  out = g / rows * d loss / d logits                                           (reads lse)
+ * op 4  loss = sum_v ((1 - t) dv - softmax(target_logits) + xst)^2 with xst as in op 1 and
+ *       dv = ddt (p - xs) + dt p o (tlogits - sum(p tlogits)), ddt = 1 / (1 - s + 1e-8); reads lse (op 1), writes stats
+ * op 5  out, out2 = g / rows * d loss / d (logits, tlogits)                          (reads lse and stats) */
+int jvpattn_vocab_op(int op, const void *logits, const void *tlogits, const void *target_logits, int64_t ld, const float *x0,
+                     int64_t ldx, const int64_t *ids, const float *s, const float *t, float *lse, float *stats, float *loss,
+                     const float *g, void *out, void *out2, int64_t ldo, float eps, int batch, int rows_per_sample, int vocab,
+                     int dtype, void *stream);
+
 /* Same backward for callers that have no way to allocate device memory (no counterpart in the reference,
  * whose wrappers allocate freely through torch).  Takes no workspace: the scratch lives in a fixed
  * 2 MiB array inside the library image, present on every GPU that loads the library until the process

@@ -1,6 +1,6 @@
 """Copy the reference's Python package into ``oracle/_ref/`` so that it can travel with a snapshot of this tree.
 
-    python oracle/make_ref.py [path to the reference checkout]        (default: /root/reference)
+    python oracle/make_ref.py [path to the reference checkout]        (default: $SEMICAT_REFERENCE, else DEFAULT_SRC)
 
 The reference (olsdavis/semicat) is pure Python and has no ``setup.py`` / ``pyproject.toml``, so it cannot be
 pip-installed; what the tests need from it is the package directory ``semicat/`` (the DiT in ``semicat/net/duo.py``,
@@ -17,9 +17,10 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
+DEFAULT_SRC = os.environ.get("SEMICAT_REFERENCE", "/root/reference")
 
 
-def make(src_root: str = "/root/reference", force: bool = False) -> str | None:
+def make(src_root: str = DEFAULT_SRC, force: bool = False) -> str | None:
     """Returns the destination directory, or None when the reference checkout is not available."""
     src = os.path.join(src_root, "semicat")
     if not os.path.isdir(src):
@@ -37,5 +38,5 @@ def make(src_root: str = "/root/reference", force: bool = False) -> str | None:
 
 
 if __name__ == "__main__":
-    out = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True)
+    out = make(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_SRC, force=True)
     print(out if out else "reference checkout not found; nothing copied")

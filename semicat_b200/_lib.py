@@ -16,7 +16,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_PKG_DIR, "csrc")
 LIB_PATH = os.path.join(_PKG_DIR, "libjvpattn.so")
 SOURCES = ["jvpattn_api.cu", "jvpattn_simt.cu", "jvpattn_sm100_fwd.cu", "jvpattn_sm100_bwd.cu",
-           "sm100_tensormap.cu", "rotary.cu", "dual_pointwise.cu", "vocab_head.cu"]
+           "sm100_tensormap.cu", "rotary.cu", "dual_pointwise.cu", "vocab_head.cu", "vocab_loss.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
@@ -30,7 +30,7 @@ EXPORTS = (
     "jvpattn_launch_count", "jvpattn_device_status", "jvpattn_strerror", "jvpattn_last_cuda_error",
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
     "jvpattn_bwd_static", "jvpattn_rotary_cast", "jvpattn_stream_check", "jvpattn_debug_set",
-    "jvpattn_ln_modulate", "jvpattn_gated_residual", "jvpattn_flow_map_head",
+    "jvpattn_ln_modulate", "jvpattn_gated_residual", "jvpattn_flow_map_head", "jvpattn_gelu_dual", "jvpattn_vocab_op",
 )
 DEBUG_WAIT_CYCLES, DEBUG_STALL_NEXT_FWD = 0, 1
 STATIC_SCRATCH_ROWS = 262144
@@ -131,6 +131,10 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_gated_residual.restype = ctypes.c_int
         lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
         lib.jvpattn_flow_map_head.restype = ctypes.c_int
+        lib.jvpattn_gelu_dual.argtypes = [I] + [V] * 5 + [I64, I, V]
+        lib.jvpattn_gelu_dual.restype = ctypes.c_int
+        lib.jvpattn_vocab_op.argtypes = [I, V, V, V, I64, V, I64] + [V] * 9 + [I64, ctypes.c_float, I, I, I, I, V]
+        lib.jvpattn_vocab_op.restype = ctypes.c_int
         lib.jvpattn_stream_check.argtypes = [ctypes.c_void_p]
         lib.jvpattn_stream_check.restype = ctypes.c_int
         lib.jvpattn_debug_set.argtypes = [ctypes.c_int, ctypes.c_longlong]

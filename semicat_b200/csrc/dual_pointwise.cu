@@ -447,6 +447,46 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(G
 constexpr int kRowsPerCta = 16;
 
 // Calls f(T{}, integral_constant<NV>) for the element type (dtype code 0 = bf16, 2 = fp32) and C / 256 in 1..4.
+
+// ------------------------------------------------------------------------------------------------ GELU (tanh form)
+// g(h) = h/2 (1 + tanh u), u = k (h + a h^3).  The MLP of the block (duo.py:118-123) applies it to a (primal, tangent)
+// pair; with T = tanh u, u' = k (1 + 3 a h^2), u'' = 6 a k h:
+//   g'  = (1 + T) / 2 + h/2 (1 - T^2) u'
+//   g'' = (1 - T^2) (u' + h/2 (u'' - 2 T u'^2))
+// mode 0: y = g(h);  mode 1: out = g'(h) * v (the tangent, and the VJP of either output with respect to its own input);
+// mode 2: out = g'(h) * v and out2 = g''(h) * w * v (the VJP of the tangent output: with respect to the tangent and to h).
+struct GeluTerms {
+  float g, d1, d2;
+};
+__device__ __forceinline__ GeluTerms gelu_terms(float h) {
+  constexpr float k = 0.7978845608028654f, a = 0.044715f;
+  const float h2 = h * h, T = tanhf(k * (h + a * h2 * h));
+  const float up = k * (1.f + 3.f * a * h2), upp = 6.f * a * k * h, sech2 = 1.f - T * T;
+  GeluTerms r;
+  r.g = 0.5f * h * (1.f + T);
+  r.d1 = 0.5f * (1.f + T) + 0.5f * h * sech2 * up;
+  r.d2 = sech2 * (up + 0.5f * h * (upp - 2.f * T * up * up));
+  return r;
+}
+
+template <typename T, int kMode>
+__global__ void __launch_bounds__(256) gelu_dual_kernel(const T *h, const T *v, const T *w, T *out, T *out2, int64_t n8) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float hv[8], vv[8], wv[8], o[8], o2[8];
+    load8<T>(h + i * 8, hv);
+    if (kMode >= 1) load8<T>(v + i * 8, vv);
+    if (kMode == 2) load8<T>(w + i * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const GeluTerms t = gelu_terms(hv[j]);
+      o[j] = kMode == 0 ? t.g : t.d1 * vv[j];
+      if (kMode == 2) o2[j] = t.d2 * wv[j] * vv[j];
+    }
+    store8<T>(out + i * 8, o);
+    if (kMode == 2) store8<T>(out2 + i * 8, o2);
+  }
+}
+
 template <typename F>
 cudaError_t dispatch(int dtype, int C, F &&f) {
   auto with_nv = [&](auto t) -> cudaError_t {
@@ -518,6 +558,30 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
     }
     return cudaGetLastError();
   });
+}
+
+cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
+                      cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  if (n % 8) return cudaErrorInvalidValue;
+  const int64_t n8 = n / 8;
+  const unsigned grid = (unsigned)std::min<int64_t>((n8 + 255) / 256, 148 * 16);
+  LaunchScope scope(kIdDual, stream);
+  auto launch = [&](auto tag) -> cudaError_t {
+    using T = decltype(tag);
+    auto H = static_cast<const T *>(h), V = static_cast<const T *>(v), W = static_cast<const T *>(w);
+    auto O = static_cast<T *>(out), O2 = static_cast<T *>(out2);
+    switch (mode) {
+      case 0: gelu_dual_kernel<T, 0><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
+      case 1: gelu_dual_kernel<T, 1><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
+      case 2: gelu_dual_kernel<T, 2><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
+      default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+  };
+  if (dtype == JVPATTN_BF16) return launch(__nv_bfloat16{});
+  if (dtype == JVPATTN_FP32) return launch(float{});
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace jvpattn

@@ -283,6 +283,39 @@ int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, in
                               rows_per_sample, vocab, dtype, static_cast<cudaStream_t>(stream)));
 }
 
+int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
+                      void *stream) {
+  if (mode < 0 || mode > 2 || n < 0 || n % 8) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if (n == 0) return JVPATTN_OK;
+  if (!h || !out || (mode >= 1 && !v) || (mode == 2 && (!w || !out2))) return JVPATTN_EINVAL;
+  for (const void *p : {h, v, w, (const void *)out, (const void *)out2})
+    if (p && reinterpret_cast<uintptr_t>(p) % 16) return JVPATTN_EALIGN;
+  return note_cuda(gelu_dual(mode, h, v, w, out, out2, n, dtype, static_cast<cudaStream_t>(stream)));
+}
+
+int jvpattn_vocab_op(int op, const void *logits, const void *tlogits, const void *target_logits, int64_t ld, const float *x0,
+                     int64_t ldx, const int64_t *ids, const float *s, const float *t, float *lse, float *stats, float *loss,
+                     const float *g, void *out, void *out2, int64_t ldo, float eps, int batch, int rows_per_sample, int vocab,
+                     int dtype, void *stream) {
+  if (op < 0 || op > 5 || batch < 0 || rows_per_sample < 0 || vocab < 1) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * rows_per_sample == 0) return JVPATTN_OK;
+  const bool ok = op == 0   ? x0 && ids && t && out
+                  : op == 1 ? logits && x0 && ids && s && t && lse && out
+                  : op == 2 ? logits && ids && lse && loss
+                  : op == 3 ? logits && ids && lse && g && out
+                  : op == 4 ? logits && tlogits && target_logits && x0 && ids && s && t && lse && stats && loss
+                            : logits && tlogits && target_logits && x0 && ids && s && t && lse && stats && g && out && out2;
+  if (!ok) return JVPATTN_EINVAL;
+  return note_cuda(vocab_loss(op, logits, tlogits, target_logits, ld, x0, ldx, ids, s, t, lse, stats, loss, g, out, out2, ldo,
+                              eps, batch, rows_per_sample, vocab, dtype, static_cast<cudaStream_t>(stream)));
+}
+
 uint64_t jvpattn_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char *jvpattn_last_cuda_error(void) { return t_cuda_error; }

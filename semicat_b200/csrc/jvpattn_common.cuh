@@ -69,6 +69,15 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
                            void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream);
 
+cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
+                      cudaStream_t stream);
+
+// vocab_loss.cu: interpolation, flow map, cross-entropy and self-distillation loss over the vocabulary axis
+cudaError_t vocab_loss(int op, const void *l, const void *tl, const void *lt, int64_t ld, const float *x0, int64_t ldx,
+                       const int64_t *ids, const float *s, const float *t, float *lse, float *stats, float *loss, const float *g,
+                       void *out, void *out2, int64_t ldo, float eps, int batch, int rows_per_sample, int V, int dtype,
+                       cudaStream_t stream);
+
 // vocab_head.cu: flow-map head over the vocabulary axis on (primal, tangent) pairs, with its VJPs
 cudaError_t vocab_head(int which, const void *l, const void *tl, int64_t ldl, int64_t ldt, const float *x, const float *dt,
                        const float *ddt, float *lse, float *out, const float *g, void *dl, void *dtl, int batch,

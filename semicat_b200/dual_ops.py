@@ -2,10 +2,11 @@
 
 Callers of ``safe_sdpa_jvp`` run the whole block under ``torch.func.jvp`` (semicat/models/semicat.py:153-157), where
 every pointwise op of semicat/net/duo.py:127-166 becomes several small kernels for the primal and several more for the
-tangent, and again for each of them in the backward.  Two ops cover most of that chain:
+tangent, and again for each of them in the backward.  Three ops cover most of that chain:
 
 * :func:`ln_modulate` - ``norm(x) * (1 + scale) + shift`` (duo.py:128-135 and :159),
-* :func:`gated_residual` - ``dropout(branch * gate) + skip`` (duo.py:157 and :160).
+* :func:`gated_residual` - ``dropout(branch * gate) + skip`` (duo.py:157 and :160),
+* :func:`gelu_tanh` - the GELU of the block's MLP (duo.py:118-123).
 
 Each is one kernel for the primal, one for the tangent (``jvp``), and one per cotangent in the backward, behind
 ``torch.autograd.Function`` s that work under ``torch.func.jvp`` and are reverse-mode differentiable with respect to the
@@ -263,6 +264,71 @@ def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor,
     if training and p > 0.0:
         mask = torch.empty_like(branch).bernoulli_(1.0 - p).div_(1.0 - p)
     return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)
+
+
+# ----------------------------------------------------------------------------------------------- GELU (tanh form)
+def _gelu_launch(mode, h, v, w, out, out2):
+    lib = _lib.load()
+    with torch.cuda.device(h.device):
+        rc = lib.jvpattn_gelu_dual(mode, _ptr(h), _ptr(v), _ptr(w), _ptr(out), _ptr(out2), h.numel(), _CODES[h.dtype], _stream(h))
+    _lib.check(rc, "jvpattn_gelu_dual")
+
+
+class _GeluTangent(torch.autograd.Function):
+    """ty = gelu'(h) th; backward: d_th = gelu'(h) g, d_h = gelu''(h) th g."""
+
+    @staticmethod
+    def forward(h, th):
+        ty = torch.empty_like(h)
+        _gelu_launch(1, h, th.contiguous(), None, ty, None)
+        return ty
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(*inputs)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        h, th = ctx.saved_tensors
+        d_th, d_h = torch.empty_like(h), torch.empty_like(h)
+        _gelu_launch(2, h, g.contiguous(), th.contiguous(), d_th, d_h)
+        return d_h, d_th
+
+
+class _Gelu(torch.autograd.Function):
+    @staticmethod
+    def forward(h):
+        y = torch.empty_like(h)
+        _gelu_launch(0, h, None, None, y, None)
+        return y
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.save_for_backward(*inputs)
+        ctx.save_for_forward(*inputs)
+
+    @staticmethod
+    def jvp(ctx, th):
+        (h,) = ctx.saved_for_forward
+        th = _nz(th)
+        return torch.zeros_like(h) if th is None else _GeluTangent.apply(h, th)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, g):
+        (h,) = ctx.saved_tensors
+        d_h = torch.empty_like(h)
+        _gelu_launch(1, h, g.contiguous(), None, d_h, None)
+        return d_h
+
+
+def gelu_tanh(h: torch.Tensor) -> torch.Tensor:
+    """``F.gelu(h, approximate="tanh")`` (the MLP of semicat/net/duo.py:118-123) as one kernel for the primal, one for the
+    tangent and one per cotangent; fp32 arithmetic, one rounding per output."""
+    if not (h.is_cuda and h.dtype in _CODES and h.is_contiguous() and h.numel() % 8 == 0 and (h.storage_offset() * h.element_size()) % 16 == 0):
+        return F.gelu(h, approximate="tanh")
+    return _Gelu.apply(h)
 
 
 # ----------------------------------------------------------------------------------------------- vocabulary-side head

@@ -24,7 +24,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .dual_ops import flow_map_head, gated_residual, ln_modulate
+from . import vocab_ops
+from .dual_ops import flow_map_head, gated_residual, gelu_tanh, ln_modulate
 from .functional import safe_sdpa_jvp
 from .rotary import apply_rotary_cast
 
@@ -38,8 +39,9 @@ def _rotate(x, cos, sin):
     return torch.cat((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
 
 
-def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0):
-    """``lin(x * in_scale)`` with the vocabulary-sized dimension padded to a multiple of 8 elements.
+def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0, keep_padding: bool = False):
+    """``lin(x * in_scale)`` with the vocabulary-sized dimension padded to a multiple of 8 elements.  ``x`` may already be
+    in the padded layout (``vocab_ops.interpolate_cast``); with ``keep_padding`` the padded output columns (zeros) stay.
 
     30522 is not a multiple of 8, so the operand rows of the embedding and head GEMMs are only 4-byte aligned and
     the BLAS library falls back to its pre-Hopper kernels for them (17 % of the step).  Zero columns / rows change
@@ -53,12 +55,13 @@ def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0):
     pad_in, pad_out = (-n_in) % 8, (-n_out) % 8
     if pad_in:
         dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
-        x, w = F.pad(x.to(dt), (0, pad_in)), F.pad(w.to(dt), (0, pad_in))
+        w = F.pad(w.to(dt), (0, pad_in))
+        x = x if x.shape[-1] == n_in + pad_in else F.pad(x.to(dt), (0, pad_in))
     if pad_out:
         w = F.pad(w, (0, 0, 0, pad_out))
         b = F.pad(b, (0, pad_out)) if b is not None else None
     y = F.linear(x, w, b)
-    return y[..., :n_out] if pad_out else y
+    return y[..., :n_out] if pad_out and not keep_padding else y
 
 
 class TimeEmbed(nn.Module):
@@ -113,7 +116,8 @@ class Block(nn.Module):
             a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2).to(q.dtype)).transpose(1, 2)
         if fused:
             x = gated_residual(x, self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)), g1, self.drop.p, self.training)
-            return gated_residual(x, self.mlp(ln_modulate(x, self.norm2, sh2, sc2)), g2, self.drop.p, self.training)
+            m = self.mlp[2](gelu_tanh(self.mlp[0](ln_modulate(x, self.norm2, sh2, sc2))))
+            return gated_residual(x, m, g2, self.drop.p, self.training)
         x = self.drop(self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)) * g1) + x
         return self.drop(self.mlp(self.norm2(x) * (1.0 + sc2) + sh2) * g2) + x
 
@@ -167,13 +171,15 @@ class DiT(nn.Module):
             nn.init.zeros_(lin.weight)
             nn.init.zeros_(lin.bias)
 
-    def forward(self, x, s, t, attention="sdpa"):
+    def forward(self, x, s, t, attention="sdpa", padded_logits=False):
+        """``x``: (B, L, V) as the reference passes it, or (B, L, padded V) 16-bit from ``vocab_ops.interpolate_cast``.
+        ``padded_logits`` keeps the head GEMM's padded output columns (zeros) for the fused vocabulary-side losses."""
         cond = F.silu(self.s_map(s)) + F.silu(self.t_map(t - s))
         h = self.embed(x, s, cond)
         for blk in self.blocks:
             h = blk(h, self.cos, self.sin, cond, attention)
         shift, scale = self.ada_out(cond)[:, None].chunk(2, dim=2)
-        return _aligned_linear(self.norm_out(h) * (1.0 + scale) + shift, self.head)
+        return _aligned_linear(self.norm_out(h) * (1.0 + scale) + shift, self.head, keep_padding=padded_logits)
 
 
 _REFERENCE_NAMES = (  # prefix in semicat/net/duo.py's DIT -> prefix here
@@ -230,12 +236,45 @@ def flow_map(net, x, s, t, attention):
 
 
 def draw_noise(x1, vocab, generator=None):
-    """The random draws of one step, separated out so that tests can inject the same draws everywhere."""
+    """The random draws of one step, separated out so that tests can inject the same draws everywhere.  On the GPU the
+    noise rows are spaced a multiple of 8 columns apart (16-byte aligned rows for the fused vocabulary-side kernels);
+    ``x0`` is the (B, L, vocab) view of that buffer."""
     B = x1.shape[0]
     dev = x1.device
-    return {"x0": torch.randn(B, x1.shape[1], vocab, device=dev, generator=generator),
+    width = vocab_ops.padded(vocab) if dev.type == "cuda" else vocab
+    return {"x0": torch.randn(B, x1.shape[1], width, device=dev, generator=generator)[..., :vocab],
             "t_vfm": torch.rand(B, device=dev, generator=generator), "t_sd": torch.rand(B, device=dev, generator=generator),
             "u_sd": torch.rand(B, device=dev, generator=generator)}
+
+
+def _fused_vocabulary_side(net, x0, attention, dtype) -> bool:
+    """The fused vocabulary-side kernels serve the dense ("naive") embedding on the GPU at vocabularies where a row is
+    worth a CTA; the plain-formula path ("math") keeps the PyTorch expressions and serves as the independent check."""
+    return (attention != "math" and isinstance(net.embed, NaiveEmbed) and x0.shape[-1] >= 512 and vocab_ops.usable(x0, dtype))
+
+
+def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dtype, label_smoothing):
+    """``model_step`` with the (B, L, V) tensors kept in one 16-bit padded layout between the noise and the two scalar
+    losses (vocab_ops): same objective, same rounding points at the network's boundary (input and logits in ``dtype``)."""
+    B = x1.shape[0]
+    x0 = noise["x0"]
+    V = x0.shape[-1]
+    vf_loss = sd_loss = None
+    if split < B:
+        t = noise["t_vfm"][split:]
+        xt = vocab_ops.interpolate_cast(x0[split:], x1[split:], t, dtype)
+        pred = net(xt, t, t, attention=primal_attention, padded_logits=True)
+        vf_loss = vocab_ops.cross_entropy_padded(pred, x1[split:], V, label_smoothing)
+    if split > 0:
+        t = noise["t_sd"][:split]
+        s = noise["u_sd"][:split] * t
+        xs = vocab_ops.interpolate_cast(x0[:split], x1[:split], s, dtype)
+        logits, tlogits = torch.func.jvp(lambda _t: net(xs, s, _t, attention=jvp_attention, padded_logits=True), (t,), (torch.ones_like(t),))
+        xst, lse = vocab_ops.flow_map_input(logits, x0[:split], x1[:split], s, t)
+        with torch.no_grad():
+            target = net(xst, t, t, attention=primal_attention, padded_logits=True)
+        sd_loss = vocab_ops.sd_lag_loss(logits, tlogits, target, x0[:split], x1[:split], s, t, lse)
+    return vf_loss, sd_loss
 
 
 def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0,
@@ -251,6 +290,9 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     # One autocast region for the whole objective: the bf16 copies of the weights that autocast makes are cached per
     # region, so the cross-entropy pass, the forward-mode pass and the no-grad target pass share one set of casts.
     with torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
+        io_dtype = autocast_dtype if autocast_dtype is not None else torch.float32
+        if _fused_vocabulary_side(net, x0, jvp_attention, io_dtype) and primal_attention != "math":
+            return _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, io_dtype, label_smoothing)
         # VFM step on the tail of the batch
         vf_loss = None
         if split < B:
