@@ -307,14 +307,16 @@ def count_step_flops(body, attn_flops):
 
 
 def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0.25, attention="jvp", use_graph=True,
-              primal_attention="lib"):
+              primal_attention="lib", global_batch=0, overlap=True):
     """Flow-map training steps of the DiT (semicat_b200/train_step.py) on uniform random tokens: global batch
     sharded over the ranks, forward-mode JVP through every attention layer for the first `sd_prop` of each
     shard, AdamW, one flat gradient all-reduce per step.  Every step copies its token ids from pinned host memory
     and writes its loss back to the host.  Returns a dict (times in ms, max over ranks)."""
     import torch
     from semicat_b200 import ddp, train_step
-    tc = TRAIN_CONFIGS[name]
+    tc = dict(TRAIN_CONFIGS[name])
+    if global_batch:
+        tc["global_batch"] = global_batch
     torch.manual_seed(1234)  # same initial weights on every rank
     net = train_step.DiT(tc["vocab"], 768, 128, 12, 12, dropout=0.1, length=tc["length"], embed_type=tc["embed"]).to(device)
     flat = ddp.FlatGradients(net.parameters())
@@ -331,7 +333,7 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
         noise = train_step.draw_noise(x1, tc["vocab"])
         flat.zero()
         vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention,
-                                       primal_attention=primal_attention)
+                                       primal_attention=primal_attention, overlap_branches=overlap)
         loss = train_step.total_loss(vf, sd)
         loss.backward()
         flat.all_reduce_mean()
@@ -553,6 +555,9 @@ def main():
     ap.add_argument("--sd-prop", type=float, default=0.25, help="share of each batch that takes the JVP step (training workloads)")
     ap.add_argument("--primal-attention", default="lib", choices=["sdpa", "lib"],
                     help="attention of the passes without tangents in the training workloads: torch SDPA or this library")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="training workloads: override the configuration's global batch (e.g. 64 = one rank's share of an 8-GPU run)")
+    ap.add_argument("--no-overlap", action="store_true", help="training workloads: run the two branches of the objective on one stream")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
@@ -770,10 +775,13 @@ def main_train(args):
     sampler = ClockSampler(local_rank)
     launches0 = _lib.launch_count()
     tr = run_train(args.workload, args.steps, max(args.warmup, 3), device, rank, world, dist,
-                   sampler, sd_prop=args.sd_prop, use_graph=not args.profile_mode, primal_attention=args.primal_attention)
+                   sampler, sd_prop=args.sd_prop, use_graph=not args.profile_mode, primal_attention=args.primal_attention,
+                   global_batch=args.global_batch, overlap=not args.no_overlap)
     ms, tokens, loss, peak_gb, mode = tr["ms_per_step"], tr["tokens_per_step"], tr["loss"], tr["peak_mem_gb"], tr["launch"]
     launched = _lib.launch_count() - launches0
-    tc = TRAIN_CONFIGS[args.workload]
+    tc = dict(TRAIN_CONFIGS[args.workload])
+    if args.global_batch:
+        tc["global_batch"] = args.global_batch
     if rank == 0:
         val = tokens / (ms * 1e-3)
         print(json.dumps({

@@ -253,18 +253,38 @@ def _fused_vocabulary_side(net, x0, attention, dtype) -> bool:
     return (attention != "math" and isinstance(net.embed, NaiveEmbed) and x0.shape[-1] >= 512 and vocab_ops.usable(x0, dtype))
 
 
-def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dtype, label_smoothing):
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device):
+    if device not in _SIDE_STREAMS:
+        _SIDE_STREAMS[device] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[device]
+
+
+def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dtype, label_smoothing, overlap=True):
     """``model_step`` with the (B, L, V) tensors kept in one 16-bit padded layout between the noise and the two scalar
-    losses (vocab_ops): same objective, same rounding points at the network's boundary (input and logits in ``dtype``)."""
+    losses (vocab_ops): same objective, same rounding points at the network's boundary (input and logits in ``dtype``).
+
+    The cross-entropy branch and the self-distillation branch share nothing but the weights, so with ``overlap`` the
+    first runs on a second stream (forward here; autograd runs each backward node on its forward's stream): at a few
+    dozen samples per GPU a single branch's kernels do not fill 148 SMs.  Captured into a CUDA graph the two streams become
+    two parallel branches of the graph."""
     B = x1.shape[0]
     x0 = noise["x0"]
     V = x0.shape[-1]
     vf_loss = sd_loss = None
+    both = 0 < split < B
+    main = torch.cuda.current_stream(x1.device)
+    side = _side_stream(x1.device) if (overlap and both) else main
     if split < B:
-        t = noise["t_vfm"][split:]
-        xt = vocab_ops.interpolate_cast(x0[split:], x1[split:], t, dtype)
-        pred = net(xt, t, t, attention=primal_attention, padded_logits=True)
-        vf_loss = vocab_ops.cross_entropy_padded(pred, x1[split:], V, label_smoothing)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            t = noise["t_vfm"][split:]
+            xt = vocab_ops.interpolate_cast(x0[split:], x1[split:], t, dtype)
+            pred = net(xt, t, t, attention=primal_attention, padded_logits=True)
+            vf_loss = vocab_ops.cross_entropy_padded(pred, x1[split:], V, label_smoothing)
+            del xt, pred
     if split > 0:
         t = noise["t_sd"][:split]
         s = noise["u_sd"][:split] * t
@@ -274,11 +294,12 @@ def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dt
         with torch.no_grad():
             target = net(xst, t, t, attention=primal_attention, padded_logits=True)
         sd_loss = vocab_ops.sd_lag_loss(logits, tlogits, target, x0[:split], x1[:split], s, t, lse)
+    main.wait_stream(side)
     return vf_loss, sd_loss
 
 
 def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0,
-               primal_attention="sdpa"):
+               primal_attention="sdpa", overlap_branches=True):
     """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L).
     ``jvp_attention`` selects the attention of the forward-mode pass, ``primal_attention`` that of the passes without
     tangents (the cross-entropy step and the no-grad target): "sdpa" is ``F.scaled_dot_product_attention`` as in the
@@ -292,7 +313,8 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     with torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
         io_dtype = autocast_dtype if autocast_dtype is not None else torch.float32
         if _fused_vocabulary_side(net, x0, jvp_attention, io_dtype) and primal_attention != "math":
-            return _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, io_dtype, label_smoothing)
+            return _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, io_dtype, label_smoothing,
+                                     overlap_branches)
         # VFM step on the tail of the batch
         vf_loss = None
         if split < B:
