@@ -134,9 +134,10 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
  * the tangent output) and ADD per-sample column sums into `sums` (fp32, (3, batch, channels) for ln: sum_s g n, sum_s g,
  * sum_s g nd with n the normalised row and nd its tangent; (2, batch, channels) for gate: sum_s mask y g, sum_s mask ty g),
  * which the caller zeroes beforehand and turns into the gradients of shift / scale / gate / gamma / beta
- * (semicat_b200/dual_ops.py).  `exact` selects the VJP of the LayerNorm tangent with respect to x: 0 reproduces PyTorch,
+ * (semicat_b200/dual_ops.py).  `exact` bit 0 selects the VJP of the LayerNorm tangent with respect to x: 0 reproduces PyTorch,
  * whose forward-mode formula for native_layer_norm treats the saved mean / rstd as constants when it is differentiated
- * again; 1 includes their dependence on x. */
+ * again; 1 includes their dependence on x.  Bit 1 (which = 3 only): add to what dx holds instead of overwriting it, so that
+ * the two backward kernels of one (primal, tangent) pair leave their sum. */
 int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
                         const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
                         float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int batch, int len,
@@ -159,12 +160,36 @@ int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, in
                           void *dtlogits, int batch, int rows_per_sample, int vocab, int dtype, void *stream);
 
 /* GELU (tanh form) of the block's MLP on a (primal, tangent) pair (semicat/net/duo.py:118-123), n contiguous elements of
- * `dtype` (n a multiple of 8, 16-byte aligned pointers).  mode 0: out = gelu(h).  mode 1: out = gelu'(h) * v - the
- * forward-mode tangent (v = tangent of h) and the VJP of either output with respect to its own input (v = cotangent).
- * mode 2: out = gelu'(h) * v and out2 = gelu''(h) * w * v - the VJP of the tangent output (v = its cotangent,
- * w = the tangent of h) with respect to the tangent (out) and to h (out2). */
-int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
-                      void *stream);
+ * `dtype` (n a multiple of 8, 16-byte aligned pointers).
+ * mode 0: out = gelu(h).
+ * mode 1: out = gelu'(h) * v - the forward-mode tangent (v = tangent of h) and the VJP of either output with respect to
+ *         its own input (v = cotangent).
+ * mode 2: out = gelu'(h) * v and out2 = gelu''(h) * w * v - the VJP of the tangent output (v = its cotangent, w = the
+ *         tangent of h) with respect to the tangent (out) and to h (out2).
+ * mode 3: out = gelu(h) and out2 = gelu'(h) * v - primal and tangent in one pass.
+ * mode 4: out = gelu'(h) * v + gelu''(h) * w * u and out2 = gelu'(h) * u - both cotangents in one pass (v on the primal
+ *         output, u on the tangent output, w = the tangent of h): out = gradient of h, out2 = gradient of the tangent. */
+int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, const void *u, void *out, void *out2, int64_t n,
+                      int dtype, void *stream);
+
+/* Gated residual on a (primal, tangent) pair in one pass each way (the merged form of jvpattn_gated_residual):
+ * which 0: z = x + m gate y and tz = tx + m (gate ty + tgate y)            (tx, ty, tgate, mask may be NULL)
+ * which 1: from cotangents gz on z and gtz on tz (either may be NULL): d_y = m (gate gz + tgate gtz), d_ty = m gate gtz,
+ *          sums[0][b] += sum_s m (y gz + ty gtz) (gradient of gate), sums[1][b] += sum_s m y gtz (gradient of tgate);
+ *          sums: fp32 (2, batch, channels), zeroed by the caller.  The skip gradients are gz and gtz themselves.
+ * channels: a multiple of 8, at most 1024. */
+int jvpattn_gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
+                                const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
+                                const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int batch, int len,
+                                int channels, int dtype, void *stream);
+
+/* Turns the column sums that jvpattn_ln_modulate's backward kernels leave (sums_y: which = 2, (2, batch, channels);
+ * sums_ty: which = 3, (3, batch, channels); either may be NULL) into the gradients of shift, scale, their tangents
+ * ((batch, channels) contiguous in `dtype`; NULL = not wanted) and of the LayerNorm weight and bias (fp32 (channels)),
+ * in one launch. */
+int jvpattn_ln_finalize(const float *sums_y, const float *sums_ty, const float *gamma, const float *beta, const void *scale,
+                        const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
+                        void *d_tscale, float *d_gamma, float *d_beta, int batch, int channels, int dtype, void *stream);
 
 /* Vocabulary-side ends of the flow-map training step with nothing of size (rows, vocab) materialised in fp32
  * (no counterpart among the reference's kernel wrappers; replaces the PyTorch passes of semicat/models/semicat.py:70-85,

@@ -31,6 +31,7 @@ EXPORTS = (
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
     "jvpattn_bwd_static", "jvpattn_rotary_cast", "jvpattn_stream_check", "jvpattn_debug_set",
     "jvpattn_ln_modulate", "jvpattn_gated_residual", "jvpattn_flow_map_head", "jvpattn_gelu_dual", "jvpattn_vocab_op",
+    "jvpattn_gated_residual_dual", "jvpattn_ln_finalize",
 )
 DEBUG_WAIT_CYCLES, DEBUG_STALL_NEXT_FWD = 0, 1
 STATIC_SCRATCH_ROWS = 262144
@@ -131,7 +132,11 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_gated_residual.restype = ctypes.c_int
         lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
         lib.jvpattn_flow_map_head.restype = ctypes.c_int
-        lib.jvpattn_gelu_dual.argtypes = [I] + [V] * 5 + [I64, I, V]
+        lib.jvpattn_gelu_dual.argtypes = [I] + [V] * 6 + [I64, I, V]
+        lib.jvpattn_gated_residual_dual.argtypes = [I] + [V] * 7 + [I64, I64] + [V] * 7 + [I, I, I, I, V]
+        lib.jvpattn_gated_residual_dual.restype = ctypes.c_int
+        lib.jvpattn_ln_finalize.argtypes = [V] * 6 + [I64, I64] + [V] * 6 + [I, I, I, V]
+        lib.jvpattn_ln_finalize.restype = ctypes.c_int
         lib.jvpattn_gelu_dual.restype = ctypes.c_int
         lib.jvpattn_vocab_op.argtypes = [I, V, V, V, I64, V, I64] + [V] * 9 + [I64, ctypes.c_float, I, I, I, I, V]
         lib.jvpattn_vocab_op.restype = ctypes.c_int

@@ -43,6 +43,12 @@ __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16 *p, flo
     f[2 * i + 1] = v.y;
   }
 }
+template <typename T> __device__ __forceinline__ float ldf(const T *p);
+template <> __device__ __forceinline__ float ldf<float>(const float *p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T *p, float v);
+template <> __device__ __forceinline__ void stf<float>(float *p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
 template <typename T>
 __device__ __forceinline__ void store8(T *p, const float (&f)[8]);
 template <>
@@ -81,7 +87,8 @@ struct LnArgs {
   float *sums;                   // [3, B, C] fp32 column sums (zeroed by the caller)
   int B, S, C;
   float eps;
-  int exact;                     // backward of the tangent: 1 = full second-order terms, 0 = mean / rstd held constant
+  int exact;                     // backward of the tangent: bit 0 = full second-order terms (else mean / rstd held constant),
+                                 // bit 1 = add to what dx holds instead of overwriting it
 };
 
 // ---- forward.  kTangent = false: y = (n gamma + beta)(1 + scale) + shift, saves mean / rstd.
@@ -331,7 +338,7 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_ker
         const float nn = n[v][i], tt = t[v][i];
         const float nd = rstd * (tt - m_t - nn * m_nt);
         o2[i] = rstd * (u - m_u - nn * m_un);
-        if (a.exact) {
+        if (a.exact & 1) {
           const float gn = -rstd * (u * m_nt + tt * m_un);
           o1[i] = rstd * ((w + gn) - (m_w + m_gn) - nn * (m_wn + m_gnn)) - rstd * nn * m_und;
         } else {
@@ -340,6 +347,12 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_ker
         part[0][v][i] += gv[v][i] * nn;
         part[1][v][i] += gv[v][i];
         part[2][v][i] += gv[v][i] * nd;
+      }
+      if (a.exact & 2) {  // dx already holds the gradient that arrived through the primal output: add to it
+        float prev[8];
+        load8<T>(dx + c0, prev);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o1[i] += prev[i];
       }
       store8<T>(dx + c0, o1);
       store8<T>(dtx + c0, o2);
@@ -446,7 +459,136 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(G
 
 constexpr int kRowsPerCta = 16;
 
-// Calls f(T{}, integral_constant<NV>) for the element type (dtype code 0 = bf16, 2 = fp32) and C / 256 in 1..4.
+// ---- gradients of the modulation tensors and of the LayerNorm weight / bias from the column sums of the two backward
+// kernels, in one launch.  p = sums of the VJP of y ([2, B, C]: sum_s g n, sum_s g), t = sums of the VJP of ty ([3, B, C]:
+// sum_s g n, sum_s g, sum_s g nd); either may be null.  One thread per channel walks the samples.
+struct LnFinalArgs {
+  const float *p, *t;
+  const float *gamma, *beta;
+  const void *scale, *tscale;
+  int64_t mod_stride, tmod_stride;
+  void *d_shift, *d_scale, *d_tshift, *d_tscale;  // [B, C] contiguous in the modulation dtype (null = not wanted)
+  float *d_gamma, *d_beta;                        // [C]
+  int B, C;
+};
+
+template <typename T>
+__global__ void ln_finalize_kernel(LnFinalArgs a) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.C) return;
+  const float gam = a.gamma[c], bet = a.beta ? a.beta[c] : 0.f;
+  float dg = 0.f, db = 0.f;
+  const int64_t BC = (int64_t)a.B * a.C;
+  for (int b = 0; b < a.B; ++b) {
+    const int64_t i = (int64_t)b * a.C + c;
+    const float sc1 = 1.f + ldf<T>(static_cast<const T *>(a.scale) + (int64_t)b * a.mod_stride + c);
+    const float tsc = a.tscale ? ldf<T>(static_cast<const T *>(a.tscale) + (int64_t)b * a.tmod_stride + c) : 0.f;
+    float d_scale = 0.f;
+    if (a.p) {
+      const float gn = a.p[i], g1 = a.p[BC + i];
+      if (a.d_shift) stf<T>(static_cast<T *>(a.d_shift) + i, g1);
+      d_scale += gam * gn + bet * g1;
+      dg += gn * sc1;
+      db += g1 * sc1;
+    }
+    if (a.t) {
+      const float gn = a.t[i], g1 = a.t[BC + i], gnd = a.t[2 * BC + i];
+      if (a.d_tshift) stf<T>(static_cast<T *>(a.d_tshift) + i, g1);
+      if (a.d_tscale) stf<T>(static_cast<T *>(a.d_tscale) + i, gam * gn + bet * g1);
+      d_scale += gam * gnd;
+      dg += gnd * sc1 + gn * tsc;
+      db += g1 * tsc;
+    }
+    if (a.d_scale) stf<T>(static_cast<T *>(a.d_scale) + i, d_scale);
+  }
+  a.d_gamma[c] = dg;
+  if (a.d_beta) a.d_beta[c] = db;
+}
+
+// ---- gated residual on a (primal, tangent) pair in one pass each way.
+//   forward   z = x + m g y,   tz = tx + m (g ty + tg y)                      (tx, ty, tg may be absent)
+//   backward  from cotangents gz on z and gtz on tz (either may be absent; the skip gradients are gz and gtz themselves):
+//             d_y = m (g gz + tg gtz),  d_ty = m g gtz,  d_g[b] += sum_s m (y gz + ty gtz),  d_tg[b] += sum_s m y gtz
+struct GateDualArgs {
+  const void *x, *tx, *y, *ty, *gate, *tgate, *mask;
+  int64_t gate_stride, tgate_stride;
+  void *z, *tz;
+  const void *gz, *gtz;
+  void *d_y, *d_ty;
+  float *sums;  // [2, B, C]: gate, tgate
+  int B, S, C;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) gated_dual_fwd_kernel(GateDualArgs a) {
+  const int64_t total = (int64_t)a.B * a.S * a.C / 8;
+  for (int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i8 < total; i8 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e = i8 * 8;
+    const int c0 = (int)(e % a.C);
+    const int b = (int)(e / ((int64_t)a.S * a.C));
+    float xv[8], txv[8], yv[8], tyv[8], gv[8], tgv[8], mv[8], o[8], to[8];
+    load8<T>(static_cast<const T *>(a.x) + e, xv);
+    load8<T>(static_cast<const T *>(a.y) + e, yv);
+    load8<T>(static_cast<const T *>(a.gate) + (int64_t)b * a.gate_stride + c0, gv);
+    if (a.tx) load8<T>(static_cast<const T *>(a.tx) + e, txv);
+    if (a.ty) load8<T>(static_cast<const T *>(a.ty) + e, tyv);
+    if (a.tgate) load8<T>(static_cast<const T *>(a.tgate) + (int64_t)b * a.tgate_stride + c0, tgv);
+    if (a.mask) load8<T>(static_cast<const T *>(a.mask) + e, mv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float m = a.mask ? mv[i] : 1.f;
+      o[i] = xv[i] + m * gv[i] * yv[i];
+      float br = 0.f;
+      if (a.ty) br += gv[i] * tyv[i];
+      if (a.tgate) br += tgv[i] * yv[i];
+      to[i] = (a.tx ? txv[i] : 0.f) + m * br;
+    }
+    store8<T>(static_cast<T *>(a.z) + e, o);
+    store8<T>(static_cast<T *>(a.tz) + e, to);
+  }
+}
+
+// One thread owns 8 adjacent channels of `rows_per_cta` rows of one sample: the column sums stay in registers and leave
+// with one atomic per channel and CTA; adjacent threads read adjacent 16-byte pieces of a row.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_dual_bwd_kernel(GateDualArgs a, int rows_per_cta) {
+  const int c0 = threadIdx.x * 8;
+  if (c0 >= a.C) return;
+  const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
+  const int b = blockIdx.x / ctas_per_sample;
+  const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
+  float gt[8], tgt[8], sg[8] = {}, stg[8] = {};
+  load8<T>(static_cast<const T *>(a.gate) + (int64_t)b * a.gate_stride + c0, gt);
+  if (a.tgate) load8<T>(static_cast<const T *>(a.tgate) + (int64_t)b * a.tgate_stride + c0, tgt);
+  const int s1 = min(a.S, s0 + rows_per_cta);
+#pragma unroll 2
+  for (int s = s0; s < s1; ++s) {
+    const int64_t e = ((int64_t)b * a.S + s) * a.C + c0;
+    float yv[8], tyv[8], mv[8], g1[8], g2[8], o1[8], o2[8];
+    load8<T>(static_cast<const T *>(a.y) + e, yv);
+    if (a.gz) load8<T>(static_cast<const T *>(a.gz) + e, g1);
+    if (a.gtz) load8<T>(static_cast<const T *>(a.gtz) + e, g2);
+    if (a.ty && a.gtz) load8<T>(static_cast<const T *>(a.ty) + e, tyv);
+    if (a.mask) load8<T>(static_cast<const T *>(a.mask) + e, mv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float m = a.mask ? mv[i] : 1.f;
+      const float mg1 = a.gz ? m * g1[i] : 0.f, mg2 = a.gtz ? m * g2[i] : 0.f;
+      o1[i] = gt[i] * mg1 + (a.tgate ? tgt[i] * mg2 : 0.f);
+      o2[i] = gt[i] * mg2;
+      sg[i] += yv[i] * mg1 + (a.ty && a.gtz ? tyv[i] * mg2 : 0.f);
+      stg[i] += yv[i] * mg2;
+    }
+    store8<T>(static_cast<T *>(a.d_y) + e, o1);
+    if (a.d_ty) store8<T>(static_cast<T *>(a.d_ty) + e, o2);
+  }
+  float *dg = a.sums + (int64_t)b * a.C + c0, *dtg = a.sums + ((int64_t)a.B + b) * a.C + c0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    atomicAdd(dg + i, sg[i]);
+    if (a.gtz) atomicAdd(dtg + i, stg[i]);
+  }
+}
 
 // ------------------------------------------------------------------------------------------------ GELU (tanh form)
 // g(h) = h/2 (1 + tanh u), u = k (h + a h^3).  The MLP of the block (duo.py:118-123) applies it to a (primal, tangent)
@@ -454,7 +596,10 @@ constexpr int kRowsPerCta = 16;
 //   g'  = (1 + T) / 2 + h/2 (1 - T^2) u'
 //   g'' = (1 - T^2) (u' + h/2 (u'' - 2 T u'^2))
 // mode 0: y = g(h);  mode 1: out = g'(h) * v (the tangent, and the VJP of either output with respect to its own input);
-// mode 2: out = g'(h) * v and out2 = g''(h) * w * v (the VJP of the tangent output: with respect to the tangent and to h).
+// mode 2: out = g'(h) * v and out2 = g''(h) * w * v (the VJP of the tangent output: with respect to the tangent and to h);
+// mode 3: out = g(h) and out2 = g'(h) * v (primal and tangent in one pass);
+// mode 4: out = g'(h) * v + g''(h) * w * u and out2 = g'(h) * u (both cotangents in one pass: v on y, u on ty, w = tangent
+//         of h; out = gradient of h, out2 = gradient of the tangent).
 struct GeluTerms {
   float g, d1, d2;
 };
@@ -470,23 +615,29 @@ __device__ __forceinline__ GeluTerms gelu_terms(float h) {
 }
 
 template <typename T, int kMode>
-__global__ void __launch_bounds__(256) gelu_dual_kernel(const T *h, const T *v, const T *w, T *out, T *out2, int64_t n8) {
+__global__ void __launch_bounds__(256) gelu_dual_kernel(const T *h, const T *v, const T *w, const T *u, T *out, T *out2,
+                                                        int64_t n8) {
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
-    float hv[8], vv[8], wv[8], o[8], o2[8];
+    float hv[8], vv[8], wv[8], uv[8], o[8], o2[8];
     load8<T>(h + i * 8, hv);
     if (kMode >= 1) load8<T>(v + i * 8, vv);
-    if (kMode == 2) load8<T>(w + i * 8, wv);
+    if (kMode == 2 || kMode == 4) load8<T>(w + i * 8, wv);
+    if (kMode == 4) load8<T>(u + i * 8, uv);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const GeluTerms t = gelu_terms(hv[j]);
-      o[j] = kMode == 0 ? t.g : t.d1 * vv[j];
-      if (kMode == 2) o2[j] = t.d2 * wv[j] * vv[j];
+      if (kMode == 0) o[j] = t.g;
+      if (kMode == 1) o[j] = t.d1 * vv[j];
+      if (kMode == 2) o[j] = t.d1 * vv[j], o2[j] = t.d2 * wv[j] * vv[j];
+      if (kMode == 3) o[j] = t.g, o2[j] = t.d1 * vv[j];
+      if (kMode == 4) o[j] = t.d1 * vv[j] + t.d2 * wv[j] * uv[j], o2[j] = t.d1 * uv[j];
     }
     store8<T>(out + i * 8, o);
-    if (kMode == 2) store8<T>(out2 + i * 8, o2);
+    if (kMode >= 2) store8<T>(out2 + i * 8, o2);
   }
 }
 
+// Calls f(T{}, integral_constant<NV>) for the element type (dtype code 0 = bf16, 2 = fp32) and C / 256 in 1..4.
 template <typename F>
 cudaError_t dispatch(int dtype, int C, F &&f) {
   auto with_nv = [&](auto t) -> cudaError_t {
@@ -560,8 +711,45 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
   });
 }
 
-cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
-                      cudaStream_t stream) {
+cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, const float *beta, const void *scale,
+                        const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
+                        void *d_tscale, float *d_gamma, float *d_beta, int B, int C, int dtype, cudaStream_t stream) {
+  if (C == 0) return cudaSuccess;
+  LnFinalArgs a{p, t, gamma, beta, scale, tscale, mod_stride, tmod_stride, d_shift, d_scale, d_tshift, d_tscale, d_gamma, d_beta, B, C};
+  LaunchScope scope(kIdDual, stream);
+  const unsigned grid = (unsigned)((C + 127) / 128);
+  if (dtype == JVPATTN_BF16) ln_finalize_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(a);
+  else if (dtype == JVPATTN_FP32) ln_finalize_kernel<float><<<grid, 128, 0, stream>>>(a);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+cudaError_t gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
+                                const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
+                                const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int B, int S, int C, int dtype,
+                                cudaStream_t stream) {
+  if ((int64_t)B * S * C == 0) return cudaSuccess;
+  if (C % 8 || C > 1024) return cudaErrorInvalidValue;
+  GateDualArgs a{x, tx, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, tz, gz, gtz, d_y, d_ty, sums, B, S, C};
+  LaunchScope scope(kIdDual, stream);
+  auto launch = [&](auto tag) -> cudaError_t {
+    using T = decltype(tag);
+    if (which == 0) {
+      const int64_t n8 = (int64_t)B * S * C / 8;
+      gated_dual_fwd_kernel<T><<<(unsigned)std::min<int64_t>((n8 + 255) / 256, 148 * 16), 256, 0, stream>>>(a);
+    } else {
+      constexpr int kRows = 8;
+      gated_dual_bwd_kernel<T><<<(unsigned)(B * ((S + kRows - 1) / kRows)), 128, 0, stream>>>(a, kRows);
+    }
+    return cudaGetLastError();
+  };
+  if (dtype == JVPATTN_BF16) return launch(__nv_bfloat16{});
+  if (dtype == JVPATTN_FP32) return launch(float{});
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, const void *u, void *out, void *out2, int64_t n,
+                      int dtype, cudaStream_t stream) {
   if (n == 0) return cudaSuccess;
   if (n % 8) return cudaErrorInvalidValue;
   const int64_t n8 = n / 8;
@@ -569,12 +757,14 @@ cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, voi
   LaunchScope scope(kIdDual, stream);
   auto launch = [&](auto tag) -> cudaError_t {
     using T = decltype(tag);
-    auto H = static_cast<const T *>(h), V = static_cast<const T *>(v), W = static_cast<const T *>(w);
+    auto H = static_cast<const T *>(h), V = static_cast<const T *>(v), W = static_cast<const T *>(w), U = static_cast<const T *>(u);
     auto O = static_cast<T *>(out), O2 = static_cast<T *>(out2);
     switch (mode) {
-      case 0: gelu_dual_kernel<T, 0><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
-      case 1: gelu_dual_kernel<T, 1><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
-      case 2: gelu_dual_kernel<T, 2><<<grid, 256, 0, stream>>>(H, V, W, O, O2, n8); break;
+      case 0: gelu_dual_kernel<T, 0><<<grid, 256, 0, stream>>>(H, V, W, U, O, O2, n8); break;
+      case 1: gelu_dual_kernel<T, 1><<<grid, 256, 0, stream>>>(H, V, W, U, O, O2, n8); break;
+      case 2: gelu_dual_kernel<T, 2><<<grid, 256, 0, stream>>>(H, V, W, U, O, O2, n8); break;
+      case 3: gelu_dual_kernel<T, 3><<<grid, 256, 0, stream>>>(H, V, W, U, O, O2, n8); break;
+      case 4: gelu_dual_kernel<T, 4><<<grid, 256, 0, stream>>>(H, V, W, U, O, O2, n8); break;
       default: return cudaErrorInvalidValue;
     }
     return cudaGetLastError();

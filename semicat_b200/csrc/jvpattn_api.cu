@@ -283,17 +283,49 @@ int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, in
                               rows_per_sample, vocab, dtype, static_cast<cudaStream_t>(stream)));
 }
 
-int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
-                      void *stream) {
-  if (mode < 0 || mode > 2 || n < 0 || n % 8) return JVPATTN_EINVAL;
+int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, const void *u, void *out, void *out2, int64_t n,
+                      int dtype, void *stream) {
+  if (mode < 0 || mode > 4 || n < 0 || n % 8) return JVPATTN_EINVAL;
   if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
   DeviceInfo *d = nullptr;
   if (int rc = current_device(&d)) return rc;
   if (n == 0) return JVPATTN_OK;
-  if (!h || !out || (mode >= 1 && !v) || (mode == 2 && (!w || !out2))) return JVPATTN_EINVAL;
-  for (const void *p : {h, v, w, (const void *)out, (const void *)out2})
+  if (!h || !out || (mode >= 1 && !v) || (mode >= 2 && !out2) || ((mode == 2 || mode == 4) && !w) || (mode == 4 && !u))
+    return JVPATTN_EINVAL;
+  for (const void *p : {h, v, w, u, (const void *)out, (const void *)out2})
     if (p && reinterpret_cast<uintptr_t>(p) % 16) return JVPATTN_EALIGN;
-  return note_cuda(gelu_dual(mode, h, v, w, out, out2, n, dtype, static_cast<cudaStream_t>(stream)));
+  return note_cuda(gelu_dual(mode, h, v, w, u, out, out2, n, dtype, static_cast<cudaStream_t>(stream)));
+}
+
+int jvpattn_ln_finalize(const float *sums_y, const float *sums_ty, const float *gamma, const float *beta, const void *scale,
+                        const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
+                        void *d_tscale, float *d_gamma, float *d_beta, int batch, int channels, int dtype, void *stream) {
+  if (batch < 0 || channels < 0) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if (!gamma || !scale || !d_gamma || (!sums_y && !sums_ty)) return JVPATTN_EINVAL;
+  return note_cuda(ln_finalize(sums_y, sums_ty, gamma, beta, scale, tscale, mod_stride, tmod_stride, d_shift, d_scale, d_tshift,
+                               d_tscale, d_gamma, d_beta, batch, channels, dtype, static_cast<cudaStream_t>(stream)));
+}
+
+int jvpattn_gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
+                                const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
+                                const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int batch, int len,
+                                int channels, int dtype, void *stream) {
+  if (which < 0 || which > 1 || batch < 0 || len < 0 || channels < 8 || channels % 8 || channels > 1024) return JVPATTN_EINVAL;
+  if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * len == 0) return JVPATTN_OK;
+  if (!y || !gate) return JVPATTN_EINVAL;
+  if (which == 0 && (!x || !z || !tz)) return JVPATTN_EINVAL;
+  if (which == 1 && ((!gz && !gtz) || !d_y || !sums || (gtz && !d_ty))) return JVPATTN_EINVAL;
+  for (const void *p : {x, tx, y, ty, gate, tgate, mask, (const void *)z, (const void *)tz, gz, gtz, (const void *)d_y, (const void *)d_ty})
+    if (p && reinterpret_cast<uintptr_t>(p) % 16) return JVPATTN_EALIGN;
+  if (gate_stride % 8 || tgate_stride % 8) return JVPATTN_EALIGN;
+  return note_cuda(gated_residual_dual(which, x, tx, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, tz, gz, gtz, d_y, d_ty,
+                                       sums, batch, len, channels, dtype, static_cast<cudaStream_t>(stream)));
 }
 
 int jvpattn_vocab_op(int op, const void *logits, const void *tlogits, const void *target_logits, int64_t ld, const float *x0,

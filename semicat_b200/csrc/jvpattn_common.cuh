@@ -69,8 +69,15 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
                            void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream);
 
-cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, void *out, void *out2, int64_t n, int dtype,
-                      cudaStream_t stream);
+cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, const float *beta, const void *scale,
+                        const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
+                        void *d_tscale, float *d_gamma, float *d_beta, int B, int C, int dtype, cudaStream_t stream);
+cudaError_t gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
+                                const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
+                                const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int B, int S, int C, int dtype,
+                                cudaStream_t stream);
+cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, const void *u, void *out, void *out2, int64_t n,
+                      int dtype, cudaStream_t stream);
 
 // vocab_loss.cu: interpolation, flow map, cross-entropy and self-distillation loss over the vocabulary axis
 cudaError_t vocab_loss(int op, const void *l, const void *tl, const void *lt, int64_t ld, const float *x0, int64_t ldx,

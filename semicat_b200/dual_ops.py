@@ -8,9 +8,11 @@ tangent, and again for each of them in the backward.  Three ops cover most of th
 * :func:`gated_residual` - ``dropout(branch * gate) + skip`` (duo.py:157 and :160),
 * :func:`gelu_tanh` - the GELU of the block's MLP (duo.py:118-123).
 
-Each is one kernel for the primal, one for the tangent (``jvp``), and one per cotangent in the backward, behind
-``torch.autograd.Function`` s that work under ``torch.func.jvp`` and are reverse-mode differentiable with respect to the
-primals AND the tangents.  CUDA only; shapes the kernels do not take (channels other than 256/512/768/1024, mixed
+Under forward-mode AD each op unpacks its dual inputs (``torch.autograd.forward_ad.unpack_dual``), runs ONE
+``torch.autograd.Function`` that maps primals and tangents to (output, output tangent), and packs the pair into a dual
+again.  Reverse mode then meets a single node per op that receives the cotangents of both outputs together, so the
+backward is one or two kernels per op with no additions of partial gradients in between.  They work under
+``torch.func.jvp`` and are reverse-mode differentiable with respect to the primals AND the tangents.  CUDA only; shapes the kernels do not take (channels other than 256/512/768/1024, mixed
 dtypes) fall back to the equivalent PyTorch expression, so callers need no special cases.
 
 ``ln_modulate`` differentiates the LayerNorm tangent like PyTorch does by default (``exact=False``): PyTorch's
@@ -20,6 +22,7 @@ the reverse pass through the tangent treats them as constants.  ``exact=True`` i
 from __future__ import annotations
 
 import torch
+import torch.autograd.forward_ad as fwAD
 import torch.nn.functional as F
 
 from . import _lib
@@ -81,46 +84,76 @@ def _ln_launch(which, x, tx, gamma, beta, shift, scale, tshift, tscale, mean, rs
     _lib.check(rc, "jvpattn_ln_modulate")
 
 
-class _LnModulateTangent(torch.autograd.Function):
-    """ty from (x, tx, scale, tshift, tscale) and the saved row statistics; backward = VJP of a cotangent on ty."""
+def _ln_finalize(sums_y, sums_ty, gamma, beta, scale, tscale, want_tangent_grads, B, C):
+    """Gradients of (shift, scale, tshift, tscale, gamma, beta) from the column sums of the backward kernels: one launch."""
+    dev, dt = scale.device, scale.dtype
+    sc, sc_stride = _rows(scale, B, C)
+    tsc, tsc_stride = _rows(tscale, B, C)
+    new = lambda: torch.empty(B, C, dtype=dt, device=dev)
+    d_shift = new() if sums_y is not None else None
+    d_scale = new()
+    d_tshift = new() if (sums_ty is not None and want_tangent_grads[0]) else None
+    d_tscale = new() if (sums_ty is not None and want_tangent_grads[1]) else None
+    d_gamma = torch.empty(C, dtype=torch.float32, device=dev)
+    d_beta = torch.empty(C, dtype=torch.float32, device=dev) if beta is not None else None
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.jvpattn_ln_finalize(_ptr(sums_y), _ptr(sums_ty), _ptr(gamma), _ptr(beta), _ptr(sc), _ptr(tsc), sc_stride, tsc_stride,
+                                     _ptr(d_shift), _ptr(d_scale), _ptr(d_tshift), _ptr(d_tscale), _ptr(d_gamma), _ptr(d_beta),
+                                     B, C, _CODES[dt], _stream(scale))
+    _lib.check(rc, "jvpattn_ln_finalize")
+    return d_shift, d_scale, d_tshift, d_tscale, d_gamma, d_beta
+
+
+class _LnModulateDual(torch.autograd.Function):
+    """(x, gamma, beta, shift, scale, tx, tshift, tscale) -> (y, ty) as one autograd node: a reverse pass brings the
+    cotangents of both outputs at once, the two backward kernels leave their sum in dx, and one more launch turns
+    their column sums into the gradients of the modulation tensors and of the LayerNorm weight and bias."""
 
     @staticmethod
-    def forward(x, tx, gamma, beta, scale, tshift, tscale, mean, rstd, eps, exact):
+    def forward(x, gamma, beta, shift, scale, tx, tshift, tscale, eps, exact):
+        B, S, C = x.shape
+        y, ty = torch.empty_like(x), torch.empty_like(x)
+        mean = torch.empty(B * S, dtype=torch.float32, device=x.device)
+        rstd = torch.empty_like(mean)
+        _ln_launch(0, x, None, gamma, beta, shift, scale, None, None, mean, rstd, y, None, None, None, None, eps, exact)
         tx_ = torch.zeros_like(x) if tx is None else tx.contiguous()
-        ty = torch.empty_like(x)
         _ln_launch(1, x, tx_, gamma, beta, None, scale, tshift, tscale, mean, rstd, ty, None, None, None, None, eps, exact)
-        return ty
+        return y, ty, mean, rstd
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        x, tx, gamma, beta, scale, tshift, tscale, mean, rstd, eps, exact = inputs
-        ctx.save_for_backward(x, tx, gamma, beta, scale, tshift, tscale, mean, rstd)
+        x, gamma, beta, shift, scale, tx, tshift, tscale, eps, exact = inputs
+        _, _, mean, rstd = output
+        ctx.mark_non_differentiable(mean, rstd)
+        ctx.save_for_backward(x, gamma, beta, shift, scale, tx, tshift, tscale, mean, rstd)
         ctx.eps, ctx.exact = eps, exact
+        ctx.set_materialize_grads(False)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
-    def backward(ctx, g):
-        x, tx, gamma, beta, scale, tshift, tscale, mean, rstd = ctx.saved_tensors
+    def backward(ctx, gy, gty, _gm, _gr):
+        if gy is None and gty is None:
+            return (None,) * 10
+        x, gamma, beta, shift, scale, tx, tshift, tscale, mean, rstd = ctx.saved_tensors
         B, S, C = x.shape
-        tx_ = torch.zeros_like(x) if tx is None else tx.contiguous()
-        dx, dtx = torch.empty_like(x), torch.empty_like(x)
-        sums = torch.zeros(3, B, C, dtype=torch.float32, device=x.device)
-        _ln_launch(3, x, tx_, gamma, None, None, scale, None, tscale, mean, rstd, None, g.contiguous(), dx, dtx, sums, ctx.eps, ctx.exact)
-        gn, g1, gnd = sums[0], sums[1], sums[2]
-        like = lambda v, ref: None if ref is None else v.to(ref.dtype).reshape(ref.shape)
-        sc32 = scale.reshape(B, C).float()
-        d_tshift = like(g1, tshift)
-        d_tscale = like(gamma * gn + (beta * g1 if beta is not None else 0.0), tscale)
-        d_scale = like(gamma * gnd, scale)
-        d_gamma = (gnd * (1.0 + sc32)).sum(0)
-        d_beta = None
-        if tscale is not None:
-            ts32 = tscale.reshape(B, C).float()
-            d_gamma = d_gamma + (gn * ts32).sum(0)
-            d_beta = (g1 * ts32).sum(0) if beta is not None else None
-        elif beta is not None:
-            d_beta = torch.zeros_like(beta)
-        return dx, (dtx if tx is not None else None), d_gamma, d_beta, d_scale, d_tshift, d_tscale, None, None, None, None
+        dx = torch.empty_like(x)
+        dtx = None
+        sums = torch.zeros(5, B, C, dtype=torch.float32, device=x.device)
+        sums_y = sums[:2] if gy is not None else None
+        sums_ty = sums[2:] if gty is not None else None
+        if gy is not None:
+            _ln_launch(2, x, None, gamma, None, None, scale, None, None, mean, rstd, None, gy.contiguous(), dx, None, sums_y, ctx.eps, ctx.exact)
+        if gty is not None:
+            tx_ = torch.zeros_like(x) if tx is None else tx.contiguous()
+            dtx = torch.empty_like(x)
+            flags = int(ctx.exact) | (2 if gy is not None else 0)
+            _ln_launch(3, x, tx_, gamma, None, None, scale, None, tscale, mean, rstd, None, gty.contiguous(), dx, dtx, sums_ty, ctx.eps, flags)
+        d_shift, d_scale, d_tshift, d_tscale, d_gamma, d_beta = _ln_finalize(
+            sums_y, sums_ty, gamma, beta, scale, tscale, (tshift is not None, tscale is not None), B, C)
+        shaped = lambda v, ref: None if v is None or ref is None else v.reshape(ref.shape)
+        return (dx, d_gamma, d_beta, shaped(d_shift, shift), shaped(d_scale, scale), dtx if tx is not None else None,
+                shaped(d_tshift, tshift), shaped(d_tscale, tscale), None, None)
 
 
 class _LnModulate(torch.autograd.Function):
@@ -139,16 +172,7 @@ class _LnModulate(torch.autograd.Function):
         _, mean, rstd = output
         ctx.mark_non_differentiable(mean, rstd)
         ctx.save_for_backward(x, gamma, beta, shift, scale, mean, rstd)
-        ctx.save_for_forward(x, gamma, beta, scale, mean, rstd)
         ctx.eps, ctx.exact = eps, exact
-
-    @staticmethod
-    def jvp(ctx, tx, tgamma, tbeta, tshift, tscale, *_):
-        # tgamma / tbeta are ignored: the LayerNorm weight and bias are parameters and carry no tangent where this is
-        # used (torch.func.jvp hands over materialised zeros for them, which cannot be told from a real tangent)
-        x, gamma, beta, scale, mean, rstd = ctx.saved_for_forward
-        ty = _LnModulateTangent.apply(x, _nz(tx), gamma, beta, scale, _nz(tshift), _nz(tscale), mean, rstd, ctx.eps, ctx.exact)
-        return ty, None, None
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -174,8 +198,14 @@ def ln_modulate(x: torch.Tensor, norm: torch.nn.LayerNorm, shift: torch.Tensor, 
     if norm.weight is None or not _usable(x, shift, scale) or tuple(norm.normalized_shape) != (x.shape[-1],):
         return norm(x) * (1.0 + scale) + shift
     beta = norm.bias.float() if norm.bias is not None else None
-    y, _, _ = _LnModulate.apply(x.contiguous(), norm.weight.float(), beta, shift, scale, norm.eps, exact)
-    return y
+    (xp, tx), (shp, tsh), (scp, tsc) = (fwAD.unpack_dual(t) for t in (x, shift, scale))
+    if tx is None and tsh is None and tsc is None:
+        y, _, _ = _LnModulate.apply(x.contiguous(), norm.weight.float(), beta, shift, scale, norm.eps, exact)
+        return y
+    # forward-mode AD is active: one node maps primals and tangents to (y, ty); the LayerNorm weight and bias are
+    # parameters and carry no tangent where this is used
+    y, ty, _, _ = _LnModulateDual.apply(xp.contiguous(), norm.weight.float(), beta, shp, scp, tx, tsh, tsc, norm.eps, exact)
+    return fwAD.make_dual(y, ty)
 
 
 def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums):
@@ -189,40 +219,52 @@ def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums):
     _lib.check(rc, "jvpattn_gated_residual")
 
 
-class _GatedResidualTangent(torch.autograd.Function):
-    """tz = tx + mask * (gate * ty + tgate * y); any of tx, ty, tgate may be absent (zero)."""
+def _gate_dual_launch(which, x, tx, y, ty, gate, tgate, mask, z, tz, gz, gtz, d_y, d_ty, sums):
+    B, S, C = y.shape
+    gt, gt_stride = _rows(gate, B, C)
+    tg, tg_stride = _rows(tgate, B, C)
+    lib = _lib.load()
+    with torch.cuda.device(y.device):
+        rc = lib.jvpattn_gated_residual_dual(which, _ptr(x), _ptr(tx), _ptr(y), _ptr(ty), _ptr(gt), _ptr(tg), _ptr(mask), gt_stride,
+                                             tg_stride, _ptr(z), _ptr(tz), _ptr(gz), _ptr(gtz), _ptr(d_y), _ptr(d_ty), _ptr(sums),
+                                             B, S, C, _CODES[y.dtype], _stream(y))
+    _lib.check(rc, "jvpattn_gated_residual_dual")
+
+
+class _GatedResidualDual(torch.autograd.Function):
+    """(x, y, gate, mask, tx, ty, tgate) -> (z, tz) = (x + m gate y, tx + m (gate ty + tgate y)) as one autograd node:
+    one kernel forward, one kernel for the cotangents of both outputs.  Any of tx, ty, tgate may be absent (zero)."""
 
     @staticmethod
-    def forward(tx, y, ty, gate, tgate, mask):
-        if ty is None and tgate is None:
-            return tx.clone() if tx is not None else torch.zeros_like(y)
-        tz = torch.empty_like(y)
+    def forward(x, y, gate, mask, tx, ty, tgate):
         c = lambda t: None if t is None else t.contiguous()
-        _gate_launch(1, c(tx), y, c(ty), gate, tgate, mask, tz, None, None, None, None)
-        return tz
+        z, tz = torch.empty_like(y), torch.empty_like(y)
+        _gate_dual_launch(0, x, c(tx), y, c(ty), gate, tgate, mask, z, tz, None, None, None, None, None)
+        return z, tz
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        tx, y, ty, gate, tgate, mask = inputs
-        ctx.save_for_backward(y, ty, gate, tgate, mask)
+        x, y, gate, mask, tx, ty, tgate = inputs
+        ctx.save_for_backward(y, gate, mask, ty, tgate)
         ctx.has_tx = tx is not None
+        ctx.set_materialize_grads(False)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
-    def backward(ctx, g):
-        y, ty, gate, tgate, mask = ctx.saved_tensors
+    def backward(ctx, gz, gtz):
+        if gz is None and gtz is None:
+            return (None,) * 7
+        y, gate, mask, ty, tgate = ctx.saved_tensors
         B, S, C = y.shape
-        g = g.contiguous()
-        d_tx = g if ctx.has_tx else None
-        if ty is None and tgate is None:
-            return d_tx, None, None, None, None, None
-        d_ty = torch.empty_like(y)
-        d_y = torch.empty_like(y) if tgate is not None else None
+        c = lambda t: None if t is None else t.contiguous()
+        gz, gtz = c(gz), c(gtz)
+        d_y = torch.empty_like(y)
+        d_ty = torch.empty_like(y) if gtz is not None else None
         sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
-        _gate_launch(2, None, y, None if ty is None else ty.contiguous(), gate, tgate, mask, None, g, d_ty, d_y, sums)
-        d_tgate = sums[0].to(tgate.dtype).reshape(tgate.shape) if tgate is not None else None
-        d_gate = sums[1].to(gate.dtype).reshape(gate.shape) if ty is not None else None
-        return d_tx, d_y, (d_ty if ty is not None else None), d_gate, d_tgate, None
+        _gate_dual_launch(1, None, None, y, c(ty), gate, tgate, mask, None, None, gz, gtz, d_y, d_ty, sums)
+        d_gate = sums[0].to(gate.dtype).reshape(gate.shape)
+        d_tgate = sums[1].to(tgate.dtype).reshape(tgate.shape) if (tgate is not None and gtz is not None) else None
+        return (gz, d_y, d_gate, None, gtz if ctx.has_tx else None, d_ty if ty is not None else None, d_tgate)
 
 
 class _GatedResidual(torch.autograd.Function):
@@ -236,12 +278,6 @@ class _GatedResidual(torch.autograd.Function):
     def setup_context(ctx, inputs, output):
         x, y, gate, mask = inputs
         ctx.save_for_backward(y, gate, mask)
-        ctx.save_for_forward(y, gate, mask)
-
-    @staticmethod
-    def jvp(ctx, tx, ty, tgate, _tmask):
-        y, gate, mask = ctx.saved_for_forward
-        return _GatedResidualTangent.apply(_nz(tx), y, _nz(ty), gate, _nz(tgate), mask)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -260,39 +296,54 @@ def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor,
     1 / (1 - p)) is drawn once and shared by primal, tangent and both backward passes."""
     if not _usable(branch, skip, gate) or skip.shape != branch.shape:
         return F.dropout(branch * gate, p, training) + skip
+    (xp, tx), (yp, ty), (gp, tg) = (fwAD.unpack_dual(t) for t in (skip, branch, gate))
     mask = None
     if training and p > 0.0:
-        mask = torch.empty_like(branch).bernoulli_(1.0 - p).div_(1.0 - p)
-    return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)
+        mask = torch.empty_like(yp).bernoulli_(1.0 - p).div_(1.0 - p)
+    if tx is None and ty is None and tg is None:
+        return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)
+    z, tz = _GatedResidualDual.apply(xp.contiguous(), yp.contiguous(), gp, mask, tx, ty, tg)
+    return fwAD.make_dual(z, tz)
 
 
 # ----------------------------------------------------------------------------------------------- GELU (tanh form)
-def _gelu_launch(mode, h, v, w, out, out2):
+def _gelu_launch(mode, h, v, w, u, out, out2):
     lib = _lib.load()
     with torch.cuda.device(h.device):
-        rc = lib.jvpattn_gelu_dual(mode, _ptr(h), _ptr(v), _ptr(w), _ptr(out), _ptr(out2), h.numel(), _CODES[h.dtype], _stream(h))
+        rc = lib.jvpattn_gelu_dual(mode, _ptr(h), _ptr(v), _ptr(w), _ptr(u), _ptr(out), _ptr(out2), h.numel(), _CODES[h.dtype], _stream(h))
     _lib.check(rc, "jvpattn_gelu_dual")
 
 
-class _GeluTangent(torch.autograd.Function):
-    """ty = gelu'(h) th; backward: d_th = gelu'(h) g, d_h = gelu''(h) th g."""
+class _GeluDual(torch.autograd.Function):
+    """(h, th) -> (gelu(h), gelu'(h) th) as one autograd node; backward: d_h = gelu'(h) gy + gelu''(h) th gty,
+    d_th = gelu'(h) gty, one kernel for whichever cotangents arrive."""
 
     @staticmethod
     def forward(h, th):
-        ty = torch.empty_like(h)
-        _gelu_launch(1, h, th.contiguous(), None, ty, None)
-        return ty
+        y, ty = torch.empty_like(h), torch.empty_like(h)
+        _gelu_launch(3, h, th.contiguous(), None, None, y, ty)
+        return y, ty
 
     @staticmethod
     def setup_context(ctx, inputs, output):
         ctx.save_for_backward(*inputs)
+        ctx.set_materialize_grads(False)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
-    def backward(ctx, g):
+    def backward(ctx, gy, gty):
+        if gy is None and gty is None:
+            return None, None
         h, th = ctx.saved_tensors
-        d_th, d_h = torch.empty_like(h), torch.empty_like(h)
-        _gelu_launch(2, h, g.contiguous(), th.contiguous(), d_th, d_h)
+        d_h = torch.empty_like(h)
+        if gty is None:
+            _gelu_launch(1, h, gy.contiguous(), None, None, d_h, None)
+            return d_h, None
+        d_th = torch.empty_like(h)
+        if gy is None:
+            _gelu_launch(2, h, gty.contiguous(), th.contiguous(), None, d_th, d_h)
+        else:
+            _gelu_launch(4, h, gy.contiguous(), th.contiguous(), gty.contiguous(), d_h, d_th)
         return d_h, d_th
 
 
@@ -300,26 +351,19 @@ class _Gelu(torch.autograd.Function):
     @staticmethod
     def forward(h):
         y = torch.empty_like(h)
-        _gelu_launch(0, h, None, None, y, None)
+        _gelu_launch(0, h, None, None, None, y, None)
         return y
 
     @staticmethod
     def setup_context(ctx, inputs, output):
         ctx.save_for_backward(*inputs)
-        ctx.save_for_forward(*inputs)
-
-    @staticmethod
-    def jvp(ctx, th):
-        (h,) = ctx.saved_for_forward
-        th = _nz(th)
-        return torch.zeros_like(h) if th is None else _GeluTangent.apply(h, th)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, g):
         (h,) = ctx.saved_tensors
         d_h = torch.empty_like(h)
-        _gelu_launch(1, h, g.contiguous(), None, d_h, None)
+        _gelu_launch(1, h, g.contiguous(), None, None, d_h, None)
         return d_h
 
 
@@ -328,7 +372,11 @@ def gelu_tanh(h: torch.Tensor) -> torch.Tensor:
     tangent and one per cotangent; fp32 arithmetic, one rounding per output."""
     if not (h.is_cuda and h.dtype in _CODES and h.is_contiguous() and h.numel() % 8 == 0 and (h.storage_offset() * h.element_size()) % 16 == 0):
         return F.gelu(h, approximate="tanh")
-    return _Gelu.apply(h)
+    hp, th = fwAD.unpack_dual(h)
+    if th is None:
+        return _Gelu.apply(h)
+    y, ty = _GeluDual.apply(hp, th)
+    return fwAD.make_dual(y, ty)
 
 
 # ----------------------------------------------------------------------------------------------- vocabulary-side head

@@ -4,31 +4,28 @@ same call contract, backed by the sm_100a kernels of ``libjvpattn.so`` instead o
 Contract kept from the reference (semicat/jvp_utils/functional.py):
 
 * ``sdpa_jvp(q, k, v)`` takes (B, H, S, D) fp16/bf16 CUDA tensors and is meant to be called under
-  forward-mode AD (``torch.func.jvp`` around the model, semicat/models/semicat.py:132-136, 153-157).
-  The plain ``forward`` only hands out the output buffer and the row-statistic buffer; the fused
-  kernel fills both when autograd calls ``jvp`` (functional.py:216-258).
+  forward-mode AD (``torch.func.jvp`` around the model, semicat/models/semicat.py:132-136, 153-157): the
+  output is a dual tensor whose primal is O and whose tangent is the JVP (functional.py:216-258).
 * The result is then reverse-mode differentiable with respect to q, k, v AND their tangents: a
-  cotangent on the tangent output runs the JVP backward (functional.py:71-87, 90-168), a cotangent on
-  the primal output runs the plain attention backward (functional.py:171-213, 260-268); autograd sums
-  the two q/k/v contributions.  A second reverse pass is refused (functional.py:166-168, 211-213).
+  cotangent on the tangent output is the JVP backward (functional.py:71-87, 90-168), a cotangent on
+  the primal output the plain attention backward (functional.py:171-213, 260-268).  Outputs that receive no
+  cotangent cost nothing (``set_materialize_grads(False)``); a second reverse pass is refused
+  (functional.py:166-168, 211-213).
 * ``safe_sdpa_jvp(q, k, v)`` takes (B, S, H, D), casts non-half inputs to bfloat16, and returns
   (B, S, H, D) in the caller's dtype (functional.py:310-332).
 
-Differences, all internal: one library call per pass instead of 1 + 6 + 2 Triton launches; the
-LI buffer (softmax denominator) of the reference is not produced because no kernel here needs it;
-the tangent output is not zero-filled before the kernel writes it.
+Differences, all internal.  The reference splits the work over three ``autograd.Function`` s (a ``forward`` that only
+hands out buffers, a ``jvp`` that fills them, one backward per cotangent: 1 + 6 + 2 Triton launches).  Here the duals
+are unpacked (``torch.autograd.forward_ad.unpack_dual``), ONE node maps (q, k, v, tq, tk, tv) to (y, ty) with one
+library call, and the pair is packed into a dual again; reverse mode reaches that node once, with whichever cotangents
+exist, and makes one library call (both cotangents go through the merged backward kernels).  The LI buffer (softmax
+denominator) of the reference is not produced because no kernel here needs it; the tangent output is not zero-filled
+before the kernel writes it.
 
 One extension: when none of q, k, v carries a forward-mode tangent, ``sdpa_jvp`` runs the primal-only instance
 of the same kernels (plain attention, reverse-mode differentiable) instead of returning an uninitialised buffer.
 The callers' non-JVP attention (the reference uses ``F.scaled_dot_product_attention`` there,
 semicat/net/duo.py:143-152) can therefore go through this library too.
-
-When both outputs receive a cotangent in one reverse pass (the ``ecld`` objective, semicat/models/semicat.py:131-151),
-autograd calls the two backward methods below separately, as it does with the reference's two Functions: two
-library calls, and autograd adds the two (dq, dk, dv) contributions.  The single merged call that handles both
-cotangents at once (``ops.jvp_attention_bwd`` with ``g_o`` and ``g_to``) is available to direct callers only: the
-tangent-side gradients must be returned by the node autograd visits first, before the cotangent of the primal output
-is known to it.
 """
 from __future__ import annotations
 
@@ -58,88 +55,51 @@ def _like_input(x: torch.Tensor) -> torch.Tensor:
     return out if out.stride(-1) == 1 else torch.empty(x.shape, dtype=x.dtype, device=x.device)
 
 
-class _AttentionWithTangent(torch.autograd.Function):
-    """Tangent half: runs the fused forward kernel.  Inputs (q, k, v, tq, tk, tv, y, lse); fills y and lse
-    in place and returns the new tensors (ty, mu).  Its backward is the VJP of a cotangent on ty."""
+class _AttentionDual(torch.autograd.Function):
+    """The fused kernel as ONE autograd node: (q, k, v, tq, tk, tv) -> (y, ty).
+
+    ``sdpa_jvp`` unpacks the forward-mode duals it is given, calls this node on primals and tangents as six ordinary
+    tensors, and packs (y, ty) into a dual again.  Reverse mode then sees a single node with two outputs, so a pass that
+    brings cotangents for both (the ``ecld`` objective, and every layer of a deep model under ``lag``: the primal output
+    feeds the layers above) runs ONE merged backward - the reference needs a call per cotangent
+    (functional.py:71-87 and :171-213) and an addition of the two (dq, dk, dv)."""
 
     @staticmethod
-    def forward(q, k, v, tq, tk, tv, y, lse):
-        ty = torch.empty_like(y)
-        rows = lse.shape[-1]
-        alloc = torch.empty if rows == q.shape[2] else torch.zeros
-        mu = alloc(lse.shape, dtype=torch.float32, device=q.device)
-        # the reference requires unit innermost stride only for the backward; the kernels here need it
-        # everywhere, so repack the rare tensor that lacks it
-        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
-        ops.jvp_attention_fwd(fix(q.detach()), fix(k.detach()), fix(v.detach()), fix(tq.detach()),
-                              fix(tk.detach()), fix(tv.detach()), y.detach(), ty, lse.detach(), mu,
-                              kernels=_kernels)
-        return ty, mu
-
-    @staticmethod
-    def setup_context(ctx, inputs, output):
-        ty, mu = output
-        ctx.save_for_backward(*inputs, ty, mu)
-        ctx.mark_non_differentiable(mu)
-        ctx.set_materialize_grads(False)
-
-    @staticmethod
-    @once_differentiable
-    def backward(ctx, g_ty, _g_mu):
-        if g_ty is None:
-            return (None,) * 8
-        q, k, v, tq, tk, tv, y, lse, ty, mu = ctx.saved_tensors
-        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
-        q, k, v, tq, tk, tv, g_ty = map(fix, (q, k, v, tq, tk, tv, g_ty))
-        grads = [_like_input(t) for t in (q, k, v, tq, tk, tv)]
-        ops.jvp_attention_bwd(q, k, v, tq, tk, tv, y, ty, None, g_ty, lse, mu, *grads, kernels=_kernels)
-        return (*grads, None, None)
-
-
-class _Attention(torch.autograd.Function):
-    """Primal half: ``forward`` allocates (y, lse) without computing; ``jvp`` triggers the fused kernel."""
-
-    @staticmethod
-    def forward(q, k, v):
+    def forward(q, k, v, tq, tk, tv):
         B, H, S, _ = q.shape
-        # (B, H, S, D) view of (B, S, H, D)-contiguous memory: the layout the denoiser wants back
-        # (duo.py:154-155 reshapes the (B, S, H, D) result to (B, S, H*D)), so that reshape stays a view.
-        # The reference hands out a (B, H, S, D)-contiguous buffer and pays a copy there; shapes are the same.
+        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
+        # (B, H, S, D) views of (B, S, H, D)-contiguous memory: the layout the denoiser wants back (duo.py:154-155
+        # reshapes the (B, S, H, D) result to (B, S, H*D)), so that reshape stays a view.
         y = torch.empty((B, S, H, v.shape[-1]), dtype=q.dtype, device=q.device).transpose(1, 2)
-        # same placeholder value as the reference (log of the key count), overwritten by the kernel
-        lse = torch.full((B, H, ops.stat_len(S)), math.log(max(k.shape[-2], 1)), dtype=torch.float32, device=q.device)
-        return y, lse
+        ty = torch.empty_like(y)
+        rows = ops.stat_len(S)
+        lse = torch.empty((B, H, rows), dtype=torch.float32, device=q.device)
+        mu = (torch.empty if rows == S else torch.zeros)((B, H, rows), dtype=torch.float32, device=q.device)
+        ops.jvp_attention_fwd(fix(q), fix(k), fix(v), fix(tq), fix(tk), fix(tv), y, ty, lse, mu, kernels=_kernels)
+        return y, ty, lse, mu
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        ctx.save_for_forward(*inputs, *output)
-        ctx.save_for_backward(*inputs, *output)
+        y, ty, lse, mu = output
+        ctx.save_for_backward(*inputs, y, ty, lse, mu)
+        ctx.mark_non_differentiable(lse, mu)
         ctx.set_materialize_grads(False)
 
     @staticmethod
-    def jvp(ctx, tq, tk, tv):
-        q, k, v, y, lse = ctx.saved_for_forward
-        # an input without a tangent has tangent zero
-        tq = torch.zeros_like(q) if tq is None else tq
-        tk = torch.zeros_like(k) if tk is None else tk
-        tv = torch.zeros_like(v) if tv is None else tv
-        ty, _ = _AttentionWithTangent.apply(q, k, v, tq, tk, tv, y, lse)
-        # the statistic output carries no meaningful tangent; like the reference (functional.py:258) the
-        # buffer itself is handed back rather than spending a kernel on zeros
-        return ty, lse
-
-    @staticmethod
     @once_differentiable
-    def backward(ctx, g_y, _g_lse):
-        if g_y is None:
-            return None, None, None
-        q, k, v, y, lse = ctx.saved_tensors
-        fix = lambda t: t if t.stride(-1) == 1 else t.contiguous()
-        q, k, v, g_y = map(fix, (q, k, v, g_y))
-        dq, dk, dv = (_like_input(t) for t in (q, k, v))
-        ops.jvp_attention_bwd(q, k, v, None, None, None, y, None, g_y, None, lse, None, dq, dk, dv,
-                              kernels=_kernels)
-        return dq, dk, dv
+    def backward(ctx, g_y, g_ty, _g_lse, _g_mu):
+        if g_y is None and g_ty is None:
+            return (None,) * 6
+        q, k, v, tq, tk, tv, y, ty, lse, mu = ctx.saved_tensors
+        fix = lambda t: t if t is None or t.stride(-1) == 1 else t.contiguous()
+        q, k, v, tq, tk, tv, g_y, g_ty = map(fix, (q, k, v, tq, tk, tv, g_y, g_ty))
+        if g_ty is None:  # only the primal output was used: plain attention backward, the tangents get no gradient
+            dq, dk, dv = (_like_input(t) for t in (q, k, v))
+            ops.jvp_attention_bwd(q, k, v, None, None, None, y, None, g_y, None, lse, None, dq, dk, dv, kernels=_kernels)
+            return dq, dk, dv, None, None, None
+        grads = [_like_input(t) for t in (q, k, v, tq, tk, tv)]
+        ops.jvp_attention_bwd(q, k, v, tq, tk, tv, y, ty, g_y, g_ty, lse, mu, *grads, kernels=_kernels)
+        return tuple(grads)
 
 
 class _PrimalAttention(torch.autograd.Function):
@@ -164,10 +124,6 @@ class _PrimalAttention(torch.autograd.Function):
         dq, dk, dv = (_like_input(t) for t in (q, k, v))
         ops.jvp_attention_bwd(q, k, v, None, None, None, y, None, g_y, None, lse, None, dq, dk, dv, kernels=_kernels)
         return dq, dk, dv
-
-
-def _carries_tangent(t: torch.Tensor) -> bool:
-    return fwAD.unpack_dual(t).tangent is not None
 
 
 def _validate(q, k, v):
@@ -196,10 +152,15 @@ def sdpa_jvp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     uninitialised buffer in that case, functional.py:286-287).
     """
     _validate(q, k, v)
-    if not (_carries_tangent(q) or _carries_tangent(k) or _carries_tangent(v)):
+    (qp, tq), (kp, tk), (vp, tv) = (fwAD.unpack_dual(t) for t in (q, k, v))
+    if tq is None and tk is None and tv is None:
         return _PrimalAttention.apply(q, k, v)
-    y, _ = _Attention.apply(q, k, v)
-    return y
+    # an input without a tangent has tangent zero
+    tq = torch.zeros_like(qp) if tq is None else tq
+    tk = torch.zeros_like(kp) if tk is None else tk
+    tv = torch.zeros_like(vp) if tv is None else tv
+    y, ty, _, _ = _AttentionDual.apply(qp, kp, vp, tq, tk, tv)
+    return fwAD.make_dual(y, ty)
 
 
 def safe_sdpa_jvp(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:

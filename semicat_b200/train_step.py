@@ -39,27 +39,42 @@ def _rotate(x, cos, sin):
     return torch.cat((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1)
 
 
+def _prepare_aligned(lin: nn.Linear, in_scale: float, dtype):
+    """Weight and bias of a vocabulary-sized ``nn.Linear`` scaled, cast and zero-padded to multiples of 8 once."""
+    w, b = lin.weight, lin.bias
+    if in_scale != 1.0:
+        w = w * in_scale
+    n_out, n_in = w.shape
+    pad_in, pad_out = (-n_in) % 8, (-n_out) % 8
+    if dtype is not None:
+        w = w.to(dtype)
+        b = b.to(dtype) if b is not None else None
+    if pad_in:
+        w = F.pad(w, (0, pad_in))
+    if pad_out:
+        w = F.pad(w, (0, 0, 0, pad_out))
+        b = F.pad(b, (0, pad_out)) if b is not None else None
+    return w, b
+
+
 def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0, keep_padding: bool = False):
     """``lin(x * in_scale)`` with the vocabulary-sized dimension padded to a multiple of 8 elements.  ``x`` may already be
     in the padded layout (``vocab_ops.interpolate_cast``); with ``keep_padding`` the padded output columns (zeros) stay.
 
     30522 is not a multiple of 8, so the operand rows of the embedding and head GEMMs are only 4-byte aligned and
     the BLAS library falls back to its pre-Hopper kernels for them (17 % of the step).  Zero columns / rows change
-    nothing in the products; ``in_scale`` is folded into the weight instead of a pass over the (B, L, V) input."""
-    w, b = lin.weight, lin.bias
-    if in_scale != 1.0:
-        w = w * in_scale
+    nothing in the products; ``in_scale`` is folded into the weight instead of a pass over the (B, L, V) input.
+    ``model_step`` prepares the padded weight once per step (``lin._prepared``) for its three passes."""
     if not x.is_cuda:
-        return F.linear(x, w, b)
-    n_out, n_in = w.shape
+        w = lin.weight * in_scale if in_scale != 1.0 else lin.weight
+        return F.linear(x, w, lin.bias)
+    n_out, n_in = lin.weight.shape
     pad_in, pad_out = (-n_in) % 8, (-n_out) % 8
-    if pad_in:
-        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else x.dtype
-        w = F.pad(w.to(dt), (0, pad_in))
-        x = x if x.shape[-1] == n_in + pad_in else F.pad(x.to(dt), (0, pad_in))
-    if pad_out:
-        w = F.pad(w, (0, 0, 0, pad_out))
-        b = F.pad(b, (0, pad_out)) if b is not None else None
+    dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else None
+    prepared = getattr(lin, "_prepared", None)
+    w, b = prepared if prepared is not None else _prepare_aligned(lin, in_scale, dt if pad_in else None)
+    if pad_in and x.shape[-1] != n_in + pad_in:
+        x = F.pad(x.to(w.dtype), (0, pad_in))
     y = F.linear(x, w, b)
     return y[..., :n_out] if pad_out and not keep_padding else y
 
@@ -298,6 +313,39 @@ def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dt
     return vf_loss, sd_loss
 
 
+class _StepCasts:
+    """The 16-bit copies of the ``nn.Linear`` parameters for one objective evaluation, made once and shared by its three
+    passes.  Autocast keeps such a cache itself, but not inside ``torch.func.jvp`` (wrapped tensors are not leaves), where
+    every use of a weight was cast again: five casts per parameter and step.  The casts are ordinary differentiable ops, so
+    a weight's gradients from the passes are summed in 16 bits and cast back to fp32 once."""
+
+    def __init__(self, net, dtype):
+        self.net, self.params, self.aligned = net, {}, []
+        if dtype is None or not next(net.parameters()).is_cuda:
+            return
+        vocab_sized = {id(net.head): 1.0}
+        if isinstance(net.embed, NaiveEmbed):
+            vocab_sized[id(net.embed.seq)] = 1.0 / net.embed.coeff
+        for mname, m in net.named_modules():
+            if not isinstance(m, nn.Linear):
+                continue
+            if id(m) in vocab_sized:
+                m._prepared = _prepare_aligned(m, vocab_sized[id(m)], dtype)
+                self.aligned.append(m)
+            else:
+                for pname, p in m.named_parameters(recurse=False):
+                    self.params[f"{mname}.{pname}"] = p.to(dtype)
+
+    def __call__(self, *args, **kwargs):
+        if not self.params:
+            return self.net(*args, **kwargs)
+        return torch.func.functional_call(self.net, self.params, args, kwargs)
+
+    def close(self):
+        for m in self.aligned:
+            m._prepared = None
+
+
 def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0,
                primal_attention="sdpa", overlap_branches=True):
     """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L).
@@ -310,9 +358,22 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     x0 = noise["x0"]
     # One autocast region for the whole objective: the bf16 copies of the weights that autocast makes are cached per
     # region, so the cross-entropy pass, the forward-mode pass and the no-grad target pass share one set of casts.
+    model = net
+    net = _StepCasts(model, autocast_dtype)  # called like the model; shares one set of 16-bit weights between the passes
+    try:
+        return _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention,
+                           overlap_branches)
+    finally:
+        net.close()
+
+
+def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention, overlap_branches):
+    B = x1.shape[0]
+    dev_type = x1.device.type
+    x0 = noise["x0"]
     with torch.autocast(dev_type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
         io_dtype = autocast_dtype if autocast_dtype is not None else torch.float32
-        if _fused_vocabulary_side(net, x0, jvp_attention, io_dtype) and primal_attention != "math":
+        if _fused_vocabulary_side(model, x0, jvp_attention, io_dtype) and primal_attention != "math":
             return _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, io_dtype, label_smoothing,
                                      overlap_branches)
         # VFM step on the tail of the batch

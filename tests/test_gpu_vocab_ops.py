@@ -138,7 +138,7 @@ def test_gelu_tanh_dual(dtype):
 
     before = _lib.launch_count()
     y, ty, (d_h, d_th) = run(dual_ops.gelu_tanh, h, th, dtype)
-    assert _lib.launch_count() - before == 4  # primal, tangent, one VJP per cotangent
+    assert _lib.launch_count() - before == 2  # one kernel for (y, ty), one for both cotangents
     ry, rty, (rd_h, rd_th) = run(lambda z: F.gelu(z, approximate="tanh"), h.double(), th.double(), torch.float64)
     tol = 1e-5 if dtype == torch.float32 else 2 ** -7
     for got, ref, name in ((y, ry, "y"), (ty, rty, "ty"), (d_h, rd_h, "d h"), (d_th, rd_th, "d th")):
