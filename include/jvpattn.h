@@ -142,9 +142,21 @@ int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *g
                         const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
                         float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int batch, int len,
                         int channels, float eps, int exact, int dtype, void *stream);
+/* Dropout keep mask generated inside the gated-residual kernels instead of read from `mask` (used when `mask` is NULL):
+ * element e of the call is kept with probability 1 - p and scaled by 1 / (1 - p); the decision is a counter-based hash
+ * (Philox-4x32-10) of (*seed, call, e / 8), so every kernel given the same three values sees the same mask - forward,
+ * tangent and backward of one call of one step.  `seed` is read from DEVICE memory at run time: draw it once per step
+ * (inside the captured graph, if there is one) and number the calls of the step with `call`. */
+typedef struct jvpattn_dropout {
+  const uint64_t *seed;
+  uint32_t call;
+  float p;
+} jvpattn_dropout;
+
 int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int batch, int len, int channels, int dtype, void *stream);
+                           void *d2, float *sums, int batch, int len, int channels, int dtype, const jvpattn_dropout *drop,
+                           void *stream);
 
 /* Vocabulary-side head of the flow-map step (no counterpart among the reference's kernel wrappers; it replaces the softmax
  * over the vocabulary and the pointwise chain around it in semicat/models/semicat.py:210-229 and its forward-mode tangent,
@@ -181,12 +193,12 @@ int jvpattn_gelu_dual(int mode, const void *h, const void *v, const void *w, con
 int jvpattn_gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
                                 const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
                                 const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int batch, int len,
-                                int channels, int dtype, void *stream);
+                                int channels, int dtype, const jvpattn_dropout *drop, void *stream);
 
 /* Turns the column sums that jvpattn_ln_modulate's backward kernels leave (sums_y: which = 2, (2, batch, channels);
  * sums_ty: which = 3, (3, batch, channels); either may be NULL) into the gradients of shift, scale, their tangents
- * ((batch, channels) contiguous in `dtype`; NULL = not wanted) and of the LayerNorm weight and bias (fp32 (channels)),
- * in one launch. */
+ * ((batch, channels) contiguous in `dtype`; NULL = not wanted) and of the LayerNorm weight and bias (fp32 (channels),
+ * zeroed by the caller: the kernel adds to them), in one launch. */
 int jvpattn_ln_finalize(const float *sums_y, const float *sums_ty, const float *gamma, const float *beta, const void *scale,
                         const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
                         void *d_tscale, float *d_gamma, float *d_beta, int batch, int channels, int dtype, void *stream);

@@ -38,6 +38,11 @@ STATIC_SCRATCH_ROWS = 262144
 NUM_KERNELS = 9
 
 
+class Dropout(ctypes.Structure):
+    """``jvpattn_dropout``: device pointer to the step's 64-bit seed, the call's number within the step, drop probability."""
+    _fields_ = [("seed", ctypes.c_void_p), ("call", ctypes.c_uint32), ("p", ctypes.c_float)]
+
+
 class Tensor4(ctypes.Structure):
     """``jvpattn_tensor``: device pointer + element strides in (batch, head, position, channel) order."""
     _fields_ = [("ptr", ctypes.c_void_p), ("stride", ctypes.c_int64 * 4)]
@@ -128,12 +133,12 @@ def load() -> ctypes.CDLL:
         V, I64, I = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
         lib.jvpattn_ln_modulate.argtypes = [I] + [V] * 8 + [I64, I64] + [V] * 7 + [I, I, I, ctypes.c_float, I, I, V]
         lib.jvpattn_ln_modulate.restype = ctypes.c_int
-        lib.jvpattn_gated_residual.argtypes = [I] + [V] * 6 + [I64, I64] + [V] * 5 + [I, I, I, I, V]
+        lib.jvpattn_gated_residual.argtypes = [I] + [V] * 6 + [I64, I64] + [V] * 5 + [I, I, I, I, ctypes.POINTER(Dropout), V]
         lib.jvpattn_gated_residual.restype = ctypes.c_int
         lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
         lib.jvpattn_flow_map_head.restype = ctypes.c_int
         lib.jvpattn_gelu_dual.argtypes = [I] + [V] * 6 + [I64, I, V]
-        lib.jvpattn_gated_residual_dual.argtypes = [I] + [V] * 7 + [I64, I64] + [V] * 7 + [I, I, I, I, V]
+        lib.jvpattn_gated_residual_dual.argtypes = [I] + [V] * 7 + [I64, I64] + [V] * 7 + [I, I, I, I, ctypes.POINTER(Dropout), V]
         lib.jvpattn_gated_residual_dual.restype = ctypes.c_int
         lib.jvpattn_ln_finalize.argtypes = [V] * 6 + [I64, I64] + [V] * 6 + [I, I, I, V]
         lib.jvpattn_ln_finalize.restype = ctypes.c_int

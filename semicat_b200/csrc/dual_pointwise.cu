@@ -365,6 +365,41 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_ker
 // ---- gated residual.  z = x + m (g y)            tz = tx + m (g ty + tg y)
 // backward of z (cotangent G):   dx = G, dy = m g G, dg[b] += sum_s m y G
 // backward of tz (cotangent G):  dtx = G, dty = m g G, dtg[b] += sum_s m y G, dy = m tg G, dg[b] += sum_s m ty G
+// ---- dropout keep mask computed in the kernel instead of read from memory.  Philox-4x32-10 (Salmon et al., "Parallel
+// random numbers: as easy as 1, 2, 3", 2011) keyed by a 64-bit seed that lives in device memory (drawn once per training
+// step, so a replayed CUDA graph sees a new one), counter = (chunk index, call index): every kernel that touches the same
+// call of the same step regenerates the same mask.  One call yields 8 x 16 bits = the masks of 8 adjacent elements.
+struct DropArgs {
+  const unsigned long long *seed;  // null: no generated mask
+  unsigned call;
+  float p;
+};
+
+__device__ __forceinline__ void dropout8(const DropArgs &d, int64_t chunk, float (&m)[8]) {
+  const unsigned long long seed = *d.seed;
+  unsigned k0 = (unsigned)seed, k1 = (unsigned)(seed >> 32);
+  unsigned c0 = (unsigned)chunk, c1 = (unsigned)((unsigned long long)chunk >> 32), c2 = d.call, c3 = 0x5eedu;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const unsigned hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  const float keep = 1.f - d.p, inv = 1.f / keep;
+  const unsigned thr = (unsigned)(keep * 65536.f);
+  const unsigned w[4] = {c0, c1, c2, c3};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m[2 * i] = (w[i] & 0xffffu) < thr ? inv : 0.f;
+    m[2 * i + 1] = (w[i] >> 16) < thr ? inv : 0.f;
+  }
+}
+
 struct GateArgs {
   const void *x, *y, *ty;    // [rows, C]; x may be null in the tangent forward without a tangent on x
   const void *gate, *tgate;  // [B, C] rows `gate_stride` / `tgate_stride` apart (tgate may be null)
@@ -375,6 +410,7 @@ struct GateArgs {
   void *d1, *d2;             // backward outputs (see the kernels)
   float *sums;               // [2, B, C]
   int B, S, C;
+  DropArgs drop;             // used when mask is null and drop.seed is not
 };
 
 // mode 0: z = x + m g y.   mode 1: tz = tx + m (g ty + tg y)  (x = tx; either of tx / tg may be absent)
@@ -391,11 +427,13 @@ __global__ void __launch_bounds__(256) gated_residual_fwd_kernel(GateArgs a) {
     float xv[8], yv[8], gv[8], mv[8], out[8];
     if (a.x) load8<XT>(static_cast<const XT *>(a.x) + e, xv);
     load8<MT>(static_cast<const MT *>(a.gate) + (int64_t)b * a.gate_stride + c0, gv);
+    const bool masked = a.mask || a.drop.seed;
     if (a.mask) load8<YT>(static_cast<const YT *>(a.mask) + e, mv);
+    else if (a.drop.seed) dropout8(a.drop, i8, mv);
     if (kMode == 0) {
       load8<YT>(static_cast<const YT *>(a.y) + e, yv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) out[i] = (a.x ? xv[i] : 0.f) + (a.mask ? mv[i] : 1.f) * gv[i] * yv[i];
+      for (int i = 0; i < 8; ++i) out[i] = (a.x ? xv[i] : 0.f) + (masked ? mv[i] : 1.f) * gv[i] * yv[i];
     } else {
       float tyv[8], tgv[8];
       if (a.ty) load8<YT>(static_cast<const YT *>(a.ty) + e, tyv);
@@ -408,7 +446,7 @@ __global__ void __launch_bounds__(256) gated_residual_fwd_kernel(GateArgs a) {
         float br = 0.f;
         if (a.ty) br += gv[i] * tyv[i];
         if (a.tgate) br += tgv[i] * yv[i];
-        out[i] = (a.x ? xv[i] : 0.f) + (a.mask ? mv[i] : 1.f) * br;
+        out[i] = (a.x ? xv[i] : 0.f) + (masked ? mv[i] : 1.f) * br;
       }
     }
     store8<XT>(static_cast<XT *>(a.z) + e, out);
@@ -439,11 +477,12 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(G
       load8<T>(static_cast<const T *>(a.y) + off + c0, yv);
       if (a.ty) load8<T>(static_cast<const T *>(a.ty) + off + c0, tyv);
       if (a.mask) load8<T>(static_cast<const T *>(a.mask) + off + c0, mv);
+      else if (a.drop.seed) dropout8(a.drop, (off + c0) / 8, mv);
       load8<T>(gate + c0, gt);
       if (tgate) load8<T>(tgate + c0, tgt);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float mg = (a.mask ? mv[i] : 1.f) * gv[i];
+        const float mg = ((a.mask || a.drop.seed) ? mv[i] : 1.f) * gv[i];
         o1[i] = mg * gt[i];
         part[0][v][i] += mg * yv[i];
         if (tgate) o2[i] = mg * tgt[i];
@@ -468,9 +507,11 @@ struct LnFinalArgs {
   const void *scale, *tscale;
   int64_t mod_stride, tmod_stride;
   void *d_shift, *d_scale, *d_tshift, *d_tscale;  // [B, C] contiguous in the modulation dtype (null = not wanted)
-  float *d_gamma, *d_beta;                        // [C]
+  float *d_gamma, *d_beta;                        // [C], zeroed by the caller: CTAs add their samples' share
   int B, C;
 };
+
+constexpr int kFinalSamples = 8;  // samples per thread of the finalize kernel
 
 template <typename T>
 __global__ void ln_finalize_kernel(LnFinalArgs a) {
@@ -479,7 +520,9 @@ __global__ void ln_finalize_kernel(LnFinalArgs a) {
   const float gam = a.gamma[c], bet = a.beta ? a.beta[c] : 0.f;
   float dg = 0.f, db = 0.f;
   const int64_t BC = (int64_t)a.B * a.C;
-  for (int b = 0; b < a.B; ++b) {
+  const int b0 = blockIdx.y * kFinalSamples, b1 = min(a.B, b0 + kFinalSamples);
+#pragma unroll 4
+  for (int b = b0; b < b1; ++b) {
     const int64_t i = (int64_t)b * a.C + c;
     const float sc1 = 1.f + ldf<T>(static_cast<const T *>(a.scale) + (int64_t)b * a.mod_stride + c);
     const float tsc = a.tscale ? ldf<T>(static_cast<const T *>(a.tscale) + (int64_t)b * a.tmod_stride + c) : 0.f;
@@ -501,8 +544,9 @@ __global__ void ln_finalize_kernel(LnFinalArgs a) {
     }
     if (a.d_scale) stf<T>(static_cast<T *>(a.d_scale) + i, d_scale);
   }
-  a.d_gamma[c] = dg;
-  if (a.d_beta) a.d_beta[c] = db;
+  // d_gamma / d_beta are zeroed by the caller (they share the zero-filled buffer of the column sums)
+  atomicAdd(a.d_gamma + c, dg);
+  if (a.d_beta) atomicAdd(a.d_beta + c, db);
 }
 
 // ---- gated residual on a (primal, tangent) pair in one pass each way.
@@ -517,6 +561,7 @@ struct GateDualArgs {
   void *d_y, *d_ty;
   float *sums;  // [2, B, C]: gate, tgate
   int B, S, C;
+  DropArgs drop;
 };
 
 template <typename T>
@@ -534,9 +579,10 @@ __global__ void __launch_bounds__(256) gated_dual_fwd_kernel(GateDualArgs a) {
     if (a.ty) load8<T>(static_cast<const T *>(a.ty) + e, tyv);
     if (a.tgate) load8<T>(static_cast<const T *>(a.tgate) + (int64_t)b * a.tgate_stride + c0, tgv);
     if (a.mask) load8<T>(static_cast<const T *>(a.mask) + e, mv);
+    else if (a.drop.seed) dropout8(a.drop, i8, mv);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float m = a.mask ? mv[i] : 1.f;
+      const float m = (a.mask || a.drop.seed) ? mv[i] : 1.f;
       o[i] = xv[i] + m * gv[i] * yv[i];
       float br = 0.f;
       if (a.ty) br += gv[i] * tyv[i];
@@ -570,9 +616,10 @@ __global__ void __launch_bounds__(128) gated_dual_bwd_kernel(GateDualArgs a, int
     if (a.gtz) load8<T>(static_cast<const T *>(a.gtz) + e, g2);
     if (a.ty && a.gtz) load8<T>(static_cast<const T *>(a.ty) + e, tyv);
     if (a.mask) load8<T>(static_cast<const T *>(a.mask) + e, mv);
+    else if (a.drop.seed) dropout8(a.drop, e / 8, mv);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      const float m = a.mask ? mv[i] : 1.f;
+      const float m = (a.mask || a.drop.seed) ? mv[i] : 1.f;
       const float mg1 = a.gz ? m * g1[i] : 0.f, mg2 = a.gtz ? m * g2[i] : 0.f;
       o1[i] = gt[i] * mg1 + (a.tgate ? tgt[i] * mg2 : 0.f);
       o2[i] = gt[i] * mg2;
@@ -690,8 +737,9 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
 
 cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream) {
-  GateArgs a{x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, B, S, C};
+                           void *d2, float *sums, int B, int S, int C, int dtype, const unsigned long long *drop_seed,
+                           unsigned drop_call, float drop_p, cudaStream_t stream) {
+  GateArgs a{x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, B, S, C, {drop_seed, drop_call, drop_p}};
   const int64_t rows = (int64_t)B * S;
   if (rows == 0) return cudaSuccess;
   LaunchScope scope(kIdDual, stream);
@@ -717,7 +765,8 @@ cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, cons
   if (C == 0) return cudaSuccess;
   LnFinalArgs a{p, t, gamma, beta, scale, tscale, mod_stride, tmod_stride, d_shift, d_scale, d_tshift, d_tscale, d_gamma, d_beta, B, C};
   LaunchScope scope(kIdDual, stream);
-  const unsigned grid = (unsigned)((C + 127) / 128);
+  if (B == 0) return cudaSuccess;
+  const dim3 grid((unsigned)((C + 127) / 128), (unsigned)((B + kFinalSamples - 1) / kFinalSamples));
   if (dtype == JVPATTN_BF16) ln_finalize_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(a);
   else if (dtype == JVPATTN_FP32) ln_finalize_kernel<float><<<grid, 128, 0, stream>>>(a);
   else return cudaErrorInvalidValue;
@@ -727,10 +776,11 @@ cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, cons
 cudaError_t gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
                                 const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
                                 const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int B, int S, int C, int dtype,
-                                cudaStream_t stream) {
+                                const unsigned long long *drop_seed, unsigned drop_call, float drop_p, cudaStream_t stream) {
   if ((int64_t)B * S * C == 0) return cudaSuccess;
   if (C % 8 || C > 1024) return cudaErrorInvalidValue;
-  GateDualArgs a{x, tx, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, tz, gz, gtz, d_y, d_ty, sums, B, S, C};
+  GateDualArgs a{x, tx, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, tz, gz, gtz, d_y, d_ty, sums, B, S, C,
+                 {drop_seed, drop_call, drop_p}};
   LaunchScope scope(kIdDual, stream);
   auto launch = [&](auto tag) -> cudaError_t {
     using T = decltype(tag);

@@ -251,8 +251,10 @@ int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *g
 
 int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int batch, int len, int channels, int dtype, void *stream) {
+                           void *d2, float *sums, int batch, int len, int channels, int dtype, const jvpattn_dropout *drop,
+                           void *stream) {
   if (which < 0 || which > 2 || !dual_shape_ok(batch, len, channels)) return JVPATTN_EINVAL;
+  if (drop && (!drop->seed || !(drop->p >= 0.f) || !(drop->p < 1.f))) return JVPATTN_EINVAL;
   if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
   DeviceInfo *d = nullptr;
   if (int rc = current_device(&d)) return rc;
@@ -263,7 +265,8 @@ int jvpattn_gated_residual(int which, const void *x, const void *y, const void *
     return JVPATTN_EINVAL;
   if (gate_stride % 8 || tgate_stride % 8) return JVPATTN_EALIGN;
   return note_cuda(gated_residual(which, x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, batch, len,
-                                  channels, dtype, static_cast<cudaStream_t>(stream)));
+                                  channels, dtype, drop ? reinterpret_cast<const unsigned long long *>(drop->seed) : nullptr,
+                                  drop ? drop->call : 0u, drop ? drop->p : 0.f, static_cast<cudaStream_t>(stream)));
 }
 
 int jvpattn_flow_map_head(int which, const void *logits, const void *tlogits, int64_t ld_logits, int64_t ld_tlogits, const float *x,
@@ -312,7 +315,8 @@ int jvpattn_ln_finalize(const float *sums_y, const float *sums_ty, const float *
 int jvpattn_gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
                                 const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
                                 const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int batch, int len,
-                                int channels, int dtype, void *stream) {
+                                int channels, int dtype, const jvpattn_dropout *drop, void *stream) {
+  if (drop && (!drop->seed || !(drop->p >= 0.f) || !(drop->p < 1.f))) return JVPATTN_EINVAL;
   if (which < 0 || which > 1 || batch < 0 || len < 0 || channels < 8 || channels % 8 || channels > 1024) return JVPATTN_EINVAL;
   if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
   DeviceInfo *d = nullptr;
@@ -325,7 +329,9 @@ int jvpattn_gated_residual_dual(int which, const void *x, const void *tx, const 
     if (p && reinterpret_cast<uintptr_t>(p) % 16) return JVPATTN_EALIGN;
   if (gate_stride % 8 || tgate_stride % 8) return JVPATTN_EALIGN;
   return note_cuda(gated_residual_dual(which, x, tx, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, tz, gz, gtz, d_y, d_ty,
-                                       sums, batch, len, channels, dtype, static_cast<cudaStream_t>(stream)));
+                                       sums, batch, len, channels, dtype,
+                                       drop ? reinterpret_cast<const unsigned long long *>(drop->seed) : nullptr,
+                                       drop ? drop->call : 0u, drop ? drop->p : 0.f, static_cast<cudaStream_t>(stream)));
 }
 
 int jvpattn_vocab_op(int op, const void *logits, const void *tlogits, const void *target_logits, int64_t ld, const float *x0,

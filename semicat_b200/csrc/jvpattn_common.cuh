@@ -67,7 +67,8 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
                         float eps, int exact, int dtype, cudaStream_t stream);
 cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
                            const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int B, int S, int C, int dtype, cudaStream_t stream);
+                           void *d2, float *sums, int B, int S, int C, int dtype, const unsigned long long *drop_seed,
+                           unsigned drop_call, float drop_p, cudaStream_t stream);
 
 cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, const float *beta, const void *scale,
                         const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
@@ -75,7 +76,7 @@ cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, cons
 cudaError_t gated_residual_dual(int which, const void *x, const void *tx, const void *y, const void *ty, const void *gate,
                                 const void *tgate, const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, void *tz,
                                 const void *gz, const void *gtz, void *d_y, void *d_ty, float *sums, int B, int S, int C, int dtype,
-                                cudaStream_t stream);
+                                const unsigned long long *drop_seed, unsigned drop_call, float drop_p, cudaStream_t stream);
 cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, const void *u, void *out, void *out2, int64_t n,
                       int dtype, cudaStream_t stream);
 

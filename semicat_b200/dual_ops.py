@@ -21,6 +21,9 @@ the reverse pass through the tangent treats them as constants.  ``exact=True`` i
 """
 from __future__ import annotations
 
+import contextlib
+import ctypes
+
 import torch
 import torch.autograd.forward_ad as fwAD
 import torch.nn.functional as F
@@ -84,8 +87,9 @@ def _ln_launch(which, x, tx, gamma, beta, shift, scale, tshift, tscale, mean, rs
     _lib.check(rc, "jvpattn_ln_modulate")
 
 
-def _ln_finalize(sums_y, sums_ty, gamma, beta, scale, tscale, want_tangent_grads, B, C):
-    """Gradients of (shift, scale, tshift, tscale, gamma, beta) from the column sums of the backward kernels: one launch."""
+def _ln_finalize(sums_y, sums_ty, gamma, beta, scale, tscale, want_tangent_grads, B, C, param_grads):
+    """Gradients of (shift, scale, tshift, tscale, gamma, beta) from the column sums of the backward kernels: one launch.
+    ``param_grads``: zeroed fp32 (2, C) that receives d_gamma and d_beta."""
     dev, dt = scale.device, scale.dtype
     sc, sc_stride = _rows(scale, B, C)
     tsc, tsc_stride = _rows(tscale, B, C)
@@ -94,8 +98,8 @@ def _ln_finalize(sums_y, sums_ty, gamma, beta, scale, tscale, want_tangent_grads
     d_scale = new()
     d_tshift = new() if (sums_ty is not None and want_tangent_grads[0]) else None
     d_tscale = new() if (sums_ty is not None and want_tangent_grads[1]) else None
-    d_gamma = torch.empty(C, dtype=torch.float32, device=dev)
-    d_beta = torch.empty(C, dtype=torch.float32, device=dev) if beta is not None else None
+    d_gamma = param_grads[0]
+    d_beta = param_grads[1] if beta is not None else None
     lib = _lib.load()
     with torch.cuda.device(dev):
         rc = lib.jvpattn_ln_finalize(_ptr(sums_y), _ptr(sums_ty), _ptr(gamma), _ptr(beta), _ptr(sc), _ptr(tsc), sc_stride, tsc_stride,
@@ -139,7 +143,8 @@ class _LnModulateDual(torch.autograd.Function):
         B, S, C = x.shape
         dx = torch.empty_like(x)
         dtx = None
-        sums = torch.zeros(5, B, C, dtype=torch.float32, device=x.device)
+        zeros = torch.zeros(5 * B * C + 2 * C, dtype=torch.float32, device=x.device)  # one fill for everything that is added to
+        sums, param_grads = zeros[:5 * B * C].view(5, B, C), zeros[5 * B * C:].view(2, C)
         sums_y = sums[:2] if gy is not None else None
         sums_ty = sums[2:] if gty is not None else None
         if gy is not None:
@@ -150,7 +155,7 @@ class _LnModulateDual(torch.autograd.Function):
             flags = int(ctx.exact) | (2 if gy is not None else 0)
             _ln_launch(3, x, tx_, gamma, None, None, scale, None, tscale, mean, rstd, None, gty.contiguous(), dx, dtx, sums_ty, ctx.eps, flags)
         d_shift, d_scale, d_tshift, d_tscale, d_gamma, d_beta = _ln_finalize(
-            sums_y, sums_ty, gamma, beta, scale, tscale, (tshift is not None, tscale is not None), B, C)
+            sums_y, sums_ty, gamma, beta, scale, tscale, (tshift is not None, tscale is not None), B, C, param_grads)
         shaped = lambda v, ref: None if v is None or ref is None else v.reshape(ref.shape)
         return (dx, d_gamma, d_beta, shaped(d_shift, shift), shaped(d_scale, scale), dtx if tx is not None else None,
                 shaped(d_tshift, tshift), shaped(d_tscale, tscale), None, None)
@@ -208,18 +213,49 @@ def ln_modulate(x: torch.Tensor, norm: torch.nn.LayerNorm, shift: torch.Tensor, 
     return fwAD.make_dual(y, ty)
 
 
-def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums):
+class _Drop:
+    """Where the dropout masks of a training step come from: a 64-bit seed in device memory, drawn once per step by
+    :func:`dropout_seed`, and the number of the call within the step.  The kernels regenerate a call's mask from the two
+    wherever they need it (forward, tangent, backward) instead of reading a mask tensor."""
+    seed: torch.Tensor | None = None
+    calls = 0
+
+
+@contextlib.contextmanager
+def dropout_seed(device):
+    """Inside this context the dropout of :func:`gated_residual` is generated in its kernels from one fresh device-side
+    seed (one tiny random draw instead of a mask tensor per call; under CUDA-graph capture the draw is part of the graph,
+    so every replay sees new masks).  Outside it a mask tensor is drawn per call."""
+    prev = (_Drop.seed, _Drop.calls)
+    _Drop.seed = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=device)
+    _Drop.calls = 0
+    try:
+        yield
+    finally:
+        _Drop.seed, _Drop.calls = prev
+
+
+def _drop_struct(drop):
+    """``drop`` = (seed tensor, call number, p) or None -> ctypes argument."""
+    if drop is None:
+        return None
+    seed, call, p = drop
+    return ctypes.byref(_lib.Dropout(seed.data_ptr(), call, p))
+
+
+def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums, drop=None):
     B, S, C = y.shape
     gt, gt_stride = _rows(gate, B, C)
     tg, tg_stride = _rows(tgate, B, C)
     lib = _lib.load()
     with torch.cuda.device(y.device):
         rc = lib.jvpattn_gated_residual(which, _ptr(x), _ptr(y), _ptr(ty), _ptr(gt), _ptr(tg), _ptr(mask), gt_stride, tg_stride,
-                                        _ptr(z), _ptr(g), _ptr(d1), _ptr(d2), _ptr(sums), B, S, C, _CODES[y.dtype], _stream(y))
+                                        _ptr(z), _ptr(g), _ptr(d1), _ptr(d2), _ptr(sums), B, S, C, _CODES[y.dtype],
+                                        _drop_struct(drop), _stream(y))
     _lib.check(rc, "jvpattn_gated_residual")
 
 
-def _gate_dual_launch(which, x, tx, y, ty, gate, tgate, mask, z, tz, gz, gtz, d_y, d_ty, sums):
+def _gate_dual_launch(which, x, tx, y, ty, gate, tgate, mask, z, tz, gz, gtz, d_y, d_ty, sums, drop=None):
     B, S, C = y.shape
     gt, gt_stride = _rows(gate, B, C)
     tg, tg_stride = _rows(tgate, B, C)
@@ -227,7 +263,7 @@ def _gate_dual_launch(which, x, tx, y, ty, gate, tgate, mask, z, tz, gz, gtz, d_
     with torch.cuda.device(y.device):
         rc = lib.jvpattn_gated_residual_dual(which, _ptr(x), _ptr(tx), _ptr(y), _ptr(ty), _ptr(gt), _ptr(tg), _ptr(mask), gt_stride,
                                              tg_stride, _ptr(z), _ptr(tz), _ptr(gz), _ptr(gtz), _ptr(d_y), _ptr(d_ty), _ptr(sums),
-                                             B, S, C, _CODES[y.dtype], _stream(y))
+                                             B, S, C, _CODES[y.dtype], _drop_struct(drop), _stream(y))
     _lib.check(rc, "jvpattn_gated_residual_dual")
 
 
@@ -236,24 +272,24 @@ class _GatedResidualDual(torch.autograd.Function):
     one kernel forward, one kernel for the cotangents of both outputs.  Any of tx, ty, tgate may be absent (zero)."""
 
     @staticmethod
-    def forward(x, y, gate, mask, tx, ty, tgate):
+    def forward(x, y, gate, mask, tx, ty, tgate, drop):
         c = lambda t: None if t is None else t.contiguous()
         z, tz = torch.empty_like(y), torch.empty_like(y)
-        _gate_dual_launch(0, x, c(tx), y, c(ty), gate, tgate, mask, z, tz, None, None, None, None, None)
+        _gate_dual_launch(0, x, c(tx), y, c(ty), gate, tgate, mask, z, tz, None, None, None, None, None, drop)
         return z, tz
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        x, y, gate, mask, tx, ty, tgate = inputs
+        x, y, gate, mask, tx, ty, tgate, drop = inputs
         ctx.save_for_backward(y, gate, mask, ty, tgate)
-        ctx.has_tx = tx is not None
+        ctx.has_tx, ctx.drop = tx is not None, drop
         ctx.set_materialize_grads(False)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, gz, gtz):
         if gz is None and gtz is None:
-            return (None,) * 7
+            return (None,) * 8
         y, gate, mask, ty, tgate = ctx.saved_tensors
         B, S, C = y.shape
         c = lambda t: None if t is None else t.contiguous()
@@ -261,23 +297,24 @@ class _GatedResidualDual(torch.autograd.Function):
         d_y = torch.empty_like(y)
         d_ty = torch.empty_like(y) if gtz is not None else None
         sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
-        _gate_dual_launch(1, None, None, y, c(ty), gate, tgate, mask, None, None, gz, gtz, d_y, d_ty, sums)
+        _gate_dual_launch(1, None, None, y, c(ty), gate, tgate, mask, None, None, gz, gtz, d_y, d_ty, sums, ctx.drop)
         d_gate = sums[0].to(gate.dtype).reshape(gate.shape)
         d_tgate = sums[1].to(tgate.dtype).reshape(tgate.shape) if (tgate is not None and gtz is not None) else None
-        return (gz, d_y, d_gate, None, gtz if ctx.has_tx else None, d_ty if ty is not None else None, d_tgate)
+        return (gz, d_y, d_gate, None, gtz if ctx.has_tx else None, d_ty if ty is not None else None, d_tgate, None)
 
 
 class _GatedResidual(torch.autograd.Function):
     @staticmethod
-    def forward(x, y, gate, mask):
+    def forward(x, y, gate, mask, drop):
         z = torch.empty_like(y)
-        _gate_launch(0, x, y, None, gate, None, mask, z, None, None, None, None)
+        _gate_launch(0, x, y, None, gate, None, mask, z, None, None, None, None, drop)
         return z
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        x, y, gate, mask = inputs
+        x, y, gate, mask, drop = inputs
         ctx.save_for_backward(y, gate, mask)
+        ctx.drop = drop
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -287,22 +324,27 @@ class _GatedResidual(torch.autograd.Function):
         g = g.contiguous()
         d_y = torch.empty_like(y)
         sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
-        _gate_launch(2, None, y, None, gate, None, mask, None, g, d_y, None, sums)
-        return g, d_y, sums[0].to(gate.dtype).reshape(gate.shape), None
+        _gate_launch(2, None, y, None, gate, None, mask, None, g, d_y, None, sums, ctx.drop)
+        return g, d_y, sums[0].to(gate.dtype).reshape(gate.shape), None, None
 
 
 def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor, p: float = 0.0, training: bool = False) -> torch.Tensor:
     """``dropout(branch * gate, p) + skip`` with ``gate`` (B, 1, C) or (B, C).  The dropout keep mask (scaled by
-    1 / (1 - p)) is drawn once and shared by primal, tangent and both backward passes."""
+    1 / (1 - p)) is shared by primal, tangent and both backward passes: a tensor drawn here, or, inside
+    :func:`dropout_seed`, regenerated by each kernel from the step's seed."""
     if not _usable(branch, skip, gate) or skip.shape != branch.shape:
         return F.dropout(branch * gate, p, training) + skip
     (xp, tx), (yp, ty), (gp, tg) = (fwAD.unpack_dual(t) for t in (skip, branch, gate))
-    mask = None
+    mask = drop = None
     if training and p > 0.0:
-        mask = torch.empty_like(yp).bernoulli_(1.0 - p).div_(1.0 - p)
+        if _Drop.seed is not None and _Drop.seed.device == yp.device:
+            drop = (_Drop.seed, _Drop.calls, float(p))  # the kernels generate this call's mask themselves
+            _Drop.calls += 1
+        else:
+            mask = torch.empty_like(yp).bernoulli_(1.0 - p).div_(1.0 - p)
     if tx is None and ty is None and tg is None:
-        return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask)
-    z, tz = _GatedResidualDual.apply(xp.contiguous(), yp.contiguous(), gp, mask, tx, ty, tg)
+        return _GatedResidual.apply(skip.contiguous(), branch.contiguous(), gate, mask, drop)
+    z, tz = _GatedResidualDual.apply(xp.contiguous(), yp.contiguous(), gp, mask, tx, ty, tg, drop)
     return fwAD.make_dual(z, tz)
 
 

@@ -18,6 +18,7 @@ to check the two models against each other).  Architecture and objective follow 
 """
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
@@ -25,7 +26,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import vocab_ops
-from .dual_ops import flow_map_head, gated_residual, gelu_tanh, ln_modulate
+from .dual_ops import dropout_seed, flow_map_head, gated_residual, gelu_tanh, ln_modulate
 from .functional import safe_sdpa_jvp
 from .rotary import apply_rotary_cast
 
@@ -360,9 +361,12 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     # region, so the cross-entropy pass, the forward-mode pass and the no-grad target pass share one set of casts.
     model = net
     net = _StepCasts(model, autocast_dtype)  # called like the model; shares one set of 16-bit weights between the passes
+    # one device-side seed for every dropout mask of the step (the fused kernels regenerate the masks from it)
+    seeded = dropout_seed(x1.device) if x1.is_cuda and jvp_attention != "math" else contextlib.nullcontext()
     try:
-        return _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention,
-                           overlap_branches)
+        with seeded:
+            return _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention,
+                               overlap_branches)
     finally:
         net.close()
 

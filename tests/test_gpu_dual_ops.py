@@ -190,3 +190,36 @@ def test_flow_map_head_matches_pytorch(dtype, V, pad):
     _close(got[1], want[1], "dv", tol, 1e-4 if dtype == torch.float32 else 1e-3)
     for name, a, b in zip(("dlogits", "dtlogits"), got[2], want[2]):
         _close(a, b, name, tol, (1e-5 if dtype == torch.float32 else 2e-2) * float(b.float().abs().max()))
+
+
+def test_generated_dropout_masks_are_consistent_between_passes_and_have_the_right_rate():
+    """Inside ``dropout_seed`` the kernels regenerate each call's keep mask from (seed, call number): forward, tangent and
+    backward of one call must see the same mask, different calls and different steps different ones."""
+    B, S, C, p = 4, 64, 768, 0.25
+    dev = "cuda"
+    x = torch.zeros(B, S, C, device=dev)
+    ones = torch.ones(B, S, C, device=dev)
+    gate = torch.ones(B, 1, C, device=dev)
+    masks = []
+    for _ in range(2):  # two "steps"
+        with dual_ops.dropout_seed(torch.device(dev)):
+            # call 0: primal-only path; z = mask, and d z / d y = mask
+            y = ones.clone().requires_grad_(True)
+            z = dual_ops.gated_residual(x, y, gate, p, True)
+            (gy,) = torch.autograd.grad(z, y, ones)
+            assert torch.equal(z.detach(), gy)
+            # call 1: (primal, tangent) path with tangent 1 on the branch only: z = tz = mask, gradients = mask
+            y2, t2 = ones.clone().requires_grad_(True), ones.clone().requires_grad_(True)
+            z2, tz2 = torch.func.jvp(lambda y_: dual_ops.gated_residual(x, y_, gate, p, True), (y2,), (t2,))
+            assert torch.equal(z2.detach(), tz2.detach())
+            g_y2, g_t2 = torch.autograd.grad([z2, tz2], [y2, t2], [ones, ones])
+            assert torch.equal(g_y2, z2.detach()) and torch.equal(g_t2, z2.detach())
+            masks += [z.detach(), z2.detach()]
+    for m in masks:
+        kept = m != 0
+        assert torch.allclose(m[kept], torch.full_like(m[kept], 1.0 / (1.0 - p)))
+        assert abs(float((~kept).float().mean()) - p) < 0.01  # 196608 draws: sigma = 0.001
+    for i in range(4):
+        for j in range(i + 1, 4):
+            assert not torch.equal(masks[i], masks[j])
+    assert _lib.device_status() == 0
