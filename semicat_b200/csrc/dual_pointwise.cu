@@ -496,7 +496,15 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(G
   flush_column_sums<2, NV>(smem_raw, part, lane, dst);
 }
 
-constexpr int kRowsPerCta = 16;
+// Rows of one sample that a CTA of the backward kernels walks before it adds its column sums to global memory.  Every CTA
+// costs one atomic per column and sum, and at a few hundred samples those atomics (millions per launch, a dozen
+// contenders per address) took longer than the rows themselves; so the count grows with the problem as long as
+// eight CTAs per SM remain.
+inline int rows_per_cta(int B, int S, int base) {
+  int rows = base;
+  while (rows < 64 && (int64_t)B * ((S + 2 * rows - 1) / (2 * rows)) >= 148 * 8) rows *= 2;
+  return rows;
+}
 
 // ---- gradients of the modulation tensors and of the LayerNorm weight / bias from the column sums of the two backward
 // kernels, in one launch.  p = sums of the VJP of y ([2, B, C]: sum_s g n, sum_s g), t = sums of the VJP of ty ([3, B, C]:
@@ -664,23 +672,36 @@ __device__ __forceinline__ GeluTerms gelu_terms(float h) {
 template <typename T, int kMode>
 __global__ void __launch_bounds__(256) gelu_dual_kernel(const T *h, const T *v, const T *w, const T *u, T *out, T *out2,
                                                         int64_t n8) {
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
-    float hv[8], vv[8], wv[8], uv[8], o[8], o2[8];
-    load8<T>(h + i * 8, hv);
-    if (kMode >= 1) load8<T>(v + i * 8, vv);
-    if (kMode == 2 || kMode == 4) load8<T>(w + i * 8, wv);
-    if (kMode == 4) load8<T>(u + i * 8, uv);
+  // two chunks per iteration: all loads of both are issued before the arithmetic, so every thread keeps two 16-byte
+  // loads per operand in flight (one was not enough to cover the memory latency at full occupancy)
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < n8; i0 += 2 * stride) {
+    const int64_t idx[2] = {i0, i0 + stride};
+    float hv[2][8], vv[2][8], wv[2][8], uv[2][8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const GeluTerms t = gelu_terms(hv[j]);
-      if (kMode == 0) o[j] = t.g;
-      if (kMode == 1) o[j] = t.d1 * vv[j];
-      if (kMode == 2) o[j] = t.d1 * vv[j], o2[j] = t.d2 * wv[j] * vv[j];
-      if (kMode == 3) o[j] = t.g, o2[j] = t.d1 * vv[j];
-      if (kMode == 4) o[j] = t.d1 * vv[j] + t.d2 * wv[j] * uv[j], o2[j] = t.d1 * uv[j];
+    for (int c = 0; c < 2; ++c) {
+      if (idx[c] >= n8) continue;
+      load8<T>(h + idx[c] * 8, hv[c]);
+      if (kMode >= 1) load8<T>(v + idx[c] * 8, vv[c]);
+      if (kMode == 2 || kMode == 4) load8<T>(w + idx[c] * 8, wv[c]);
+      if (kMode == 4) load8<T>(u + idx[c] * 8, uv[c]);
     }
-    store8<T>(out + i * 8, o);
-    if (kMode >= 2) store8<T>(out2 + i * 8, o2);
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      if (idx[c] >= n8) continue;
+      float o[8], o2[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const GeluTerms t = gelu_terms(hv[c][j]);
+        if (kMode == 0) o[j] = t.g;
+        if (kMode == 1) o[j] = t.d1 * vv[c][j];
+        if (kMode == 2) o[j] = t.d1 * vv[c][j], o2[j] = t.d2 * wv[c][j] * vv[c][j];
+        if (kMode == 3) o[j] = t.g, o2[j] = t.d1 * vv[c][j];
+        if (kMode == 4) o[j] = t.d1 * vv[c][j] + t.d2 * wv[c][j] * uv[c][j], o2[j] = t.d1 * uv[c][j];
+      }
+      store8<T>(out + idx[c] * 8, o);
+      if (kMode >= 2) store8<T>(out2 + idx[c] * 8, o2);
+    }
   }
 }
 
@@ -721,14 +742,15 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
       if (which == 0) ln_modulate_fwd_kernel<T, NV, false><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
       else ln_modulate_fwd_kernel<T, NV, true><<<grid, kWarpsPerCta * 32, 0, stream>>>(a);
     } else {
-      const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
+      const int rows_cta = rows_per_cta(B, S, 16);
+      const unsigned grid = (unsigned)(B * ((S + rows_cta - 1) / rows_cta));
       if (which == 2) {
-        ln_modulate_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+        ln_modulate_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, rows_cta);
       } else {
         auto k = ln_modulate_bwd_tangent_kernel<T, NV>;
         constexpr int smem = kWarpsPerCta * 3 * NV * 256 * 4;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        k<<<grid, kWarpsPerCta * 32, smem, stream>>>(a, kRowsPerCta);
+        k<<<grid, kWarpsPerCta * 32, smem, stream>>>(a, rows_cta);
       }
     }
     return cudaGetLastError();
@@ -752,8 +774,9 @@ cudaError_t gated_residual(int which, const void *x, const void *y, const void *
       if (which == 0) gated_residual_fwd_kernel<T, 0><<<grid, 256, 0, stream>>>(a);
       else gated_residual_fwd_kernel<T, 1><<<grid, 256, 0, stream>>>(a);
     } else {
-      const unsigned grid = (unsigned)(B * ((S + kRowsPerCta - 1) / kRowsPerCta));
-      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, kRowsPerCta);
+      const int rows_cta = rows_per_cta(B, S, 16);
+      const unsigned grid = (unsigned)(B * ((S + rows_cta - 1) / rows_cta));
+      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, rows_cta);
     }
     return cudaGetLastError();
   });
@@ -788,8 +811,8 @@ cudaError_t gated_residual_dual(int which, const void *x, const void *tx, const 
       const int64_t n8 = (int64_t)B * S * C / 8;
       gated_dual_fwd_kernel<T><<<(unsigned)std::min<int64_t>((n8 + 255) / 256, 148 * 16), 256, 0, stream>>>(a);
     } else {
-      constexpr int kRows = 8;
-      gated_dual_bwd_kernel<T><<<(unsigned)(B * ((S + kRows - 1) / kRows)), 128, 0, stream>>>(a, kRows);
+      const int rows_cta = rows_per_cta(B, S, 8);
+      gated_dual_bwd_kernel<T><<<(unsigned)(B * ((S + rows_cta - 1) / rows_cta)), 128, 0, stream>>>(a, rows_cta);
     }
     return cudaGetLastError();
   };
@@ -803,7 +826,7 @@ cudaError_t gelu_dual(int mode, const void *h, const void *v, const void *w, con
   if (n == 0) return cudaSuccess;
   if (n % 8) return cudaErrorInvalidValue;
   const int64_t n8 = n / 8;
-  const unsigned grid = (unsigned)std::min<int64_t>((n8 + 255) / 256, 148 * 16);
+  const unsigned grid = (unsigned)std::min<int64_t>((n8 + 511) / 512, 148 * 8);
   LaunchScope scope(kIdDual, stream);
   auto launch = [&](auto tag) -> cudaError_t {
     using T = decltype(tag);

@@ -324,7 +324,7 @@ class _GatedResidual(torch.autograd.Function):
         g = g.contiguous()
         d_y = torch.empty_like(y)
         sums = torch.zeros(2, B, C, dtype=torch.float32, device=y.device)
-        _gate_launch(2, None, y, None, gate, None, mask, None, g, d_y, None, sums, ctx.drop)
+        _gate_dual_launch(1, None, None, y, None, gate, None, mask, None, None, g, None, d_y, None, sums, ctx.drop)
         return g, d_y, sums[0].to(gate.dtype).reshape(gate.shape), None, None
 
 
