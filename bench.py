@@ -320,6 +320,7 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     torch.manual_seed(1234)  # same initial weights on every rank
     net = train_step.DiT(tc["vocab"], 768, 128, 12, 12, dropout=0.1, length=tc["length"], embed_type=tc["embed"]).to(device)
     flat = ddp.FlatGradients(net.parameters())
+    buckets = flat.overlap_buckets(4) if (dist is not None and overlap) else 0  # exchange overlapped with the backward
     opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True, capturable=True)
     lo, hi = ddp.shard_bounds(tc["global_batch"], rank, world)
     gen = torch.Generator().manual_seed(99 + rank)
@@ -402,7 +403,8 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             dist.barrier()
             a.record()
-            flat.all_reduce_mean()
+            dist.all_reduce(flat.flat)  # the whole buffer as one message, whatever the step itself does
+            flat.flat.div_(world)
             b.record()
             b.synchronize()
             ar.append(a.elapsed_time(b))
@@ -422,7 +424,7 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     del net, opt, flat
     torch.cuda.empty_cache()
     return {"ms_per_step": ms, "ms_per_step_median": med, "tokens_per_step": tc["global_batch"] * tc["length"],
-            "loss": last_loss, "peak_mem_gb": peak_gb, "launch": mode, "allreduce_ms": ar_ms, "allreduce_bytes": nbytes,
+            "loss": last_loss, "peak_mem_gb": peak_gb, "launch": mode, "allreduce_ms": ar_ms, "allreduce_bytes": nbytes, "allreduce_buckets": buckets,
             "flops_per_step": step_flops, "steps": steps, "warmup": max(warmup, 3), "primal_attention": primal_attention,
             "device_status": status, "ms_per_step_max": max(per_step), "ms_per_step_min": min(per_step)}
 
@@ -437,6 +439,8 @@ def train_block(r, world, pk, label):
             "primal_attention": r["primal_attention"], "device_status": r["device_status"],
             "ms_per_step_min": r["ms_per_step_min"], "ms_per_step_max": r["ms_per_step_max"],
             "allreduce_ms": r["allreduce_ms"], "allreduce_bytes": r["allreduce_bytes"],
+            "allreduce_in_step": (f"{r['allreduce_buckets']} buckets, each sent on a second stream when its last gradient is accumulated"
+                                  if r["allreduce_buckets"] else "one message after the backward"),
             "flops_per_step": r["flops_per_step"], "flops_source": "torch.utils.flop_counter over one eager step + algorithmic "
             "FLOPs of the library's attention calls", "tflops": tf, "frac_of_bf16_peak": tf / (world * pk["bf16_tflops"])}
 
@@ -557,7 +561,8 @@ def main():
                     help="attention of the passes without tangents in the training workloads: torch SDPA or this library")
     ap.add_argument("--global-batch", type=int, default=0,
                     help="training workloads: override the configuration's global batch (e.g. 64 = one rank's share of an 8-GPU run)")
-    ap.add_argument("--no-overlap", action="store_true", help="training workloads: run the two branches of the objective on one stream")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="training workloads: one stream for both branches of the objective and one all-reduce after the backward")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")

@@ -3,9 +3,11 @@ ranks, one gradient all-reduce (SUM, then / world) per optimiser step over NCCL.
 reference gets from Lightning's ``strategy: ddp`` (configs/trainer/ddp.yaml:4-9); the attention kernels are
 oblivious to it, and nothing else is exchanged between ranks.
 
-Gradients live in one flat fp32 buffer (every ``p.grad`` is a view into it), so the exchange is a single
-large NCCL all-reduce with no packing copies; over NVSwitch the cost is bandwidth of one 0.4-0.6 GB message,
-about 1-2 ms next to a step of hundreds of milliseconds, so it is not split into overlapped buckets.
+Gradients live in one flat fp32 buffer (every ``p.grad`` is a view into it), so the exchange needs no packing
+copies.  As one message it takes about 1.6 ms over NVSwitch (0.56 GB); with the step down to some 20 ms per GPU that
+is worth hiding, so ``FlatGradients.overlap_buckets(n)`` splits the buffer into contiguous buckets and all-reduces
+each on a second stream as soon as autograd has accumulated the last gradient in it.  Parameters sit in the buffer in
+forward order, so the buckets complete from the back (output head first, embedding last).
 """
 from __future__ import annotations
 
@@ -58,15 +60,75 @@ class FlatGradients:
             p.grad = self.flat[off:off + p.numel()].view_as(p)
             off += p.numel()
 
+        self._buckets = None
+
     def zero(self):
         self.flat.zero_()
+        if self._buckets is not None:
+            self._pending = [len(b[2]) for b in self._buckets]
+            self._sent = [False] * len(self._buckets)
+
+    # ---- overlapped exchange -------------------------------------------------------------------------------------
+    def overlap_buckets(self, n_buckets: int = 4):
+        """Split the flat buffer into ``n_buckets`` contiguous parts of about equal size (on parameter boundaries) and
+        all-reduce each as soon as its last gradient has been accumulated during ``backward()``, on a second stream
+        (CUDA) or in place (CPU).  Call :meth:`zero` before every backward and :meth:`all_reduce_mean` after it: it sends
+        what the hooks did not (buckets with a parameter that received no gradient) and joins the second stream."""
+        if self._buckets is not None:
+            raise RuntimeError("overlap_buckets() was already called")
+        total, target = self.flat.numel(), self.flat.numel() / max(n_buckets, 1)
+        buckets, start, off, members = [], 0, 0, []
+        for p in self.params:
+            members.append(p)
+            off += p.numel()
+            if off - start >= target and len(buckets) < n_buckets - 1:
+                buckets.append((start, off, members))
+                start, members = off, []
+        if members:
+            buckets.append((start, total, members))
+        self._buckets = buckets
+        self._comm = torch.cuda.Stream(self.flat.device) if self.flat.is_cuda else None
+        for i, (_, _, ps) in enumerate(buckets):
+            for p in ps:
+                p.register_post_accumulate_grad_hook(lambda _p, i=i: self._accumulated(i))
+        self.zero()
+        return len(buckets)
+
+    def _active(self) -> bool:
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+
+    def _accumulated(self, i: int):
+        self._pending[i] -= 1
+        if self._pending[i] == 0 and self._active():
+            self._send(i)
+
+    def _send(self, i: int):
+        lo, hi, _ = self._buckets[i]
+        part = self.flat[lo:hi]
+        world = dist.get_world_size(self.group)
+        self._sent[i] = True
+        if self._comm is None:
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+            part.div_(world)
+            return
+        self._comm.wait_stream(torch.cuda.current_stream(self.flat.device))  # the accumulations into this bucket
+        with torch.cuda.stream(self._comm):
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+            part.div_(world)
 
     def all_reduce_mean(self, check_finite_on_host: bool = False):
         """Average the gradients over the ranks in place.  No-op without a process group."""
-        if not dist.is_available() or not dist.is_initialized():
+        if not self._active():
             return
         world = dist.get_world_size(self.group)
-        if world == 1:
+        if self._buckets is not None:
+            for i in range(len(self._buckets)):
+                if not self._sent[i]:
+                    self._send(i)
+            if self._comm is not None:
+                torch.cuda.current_stream(self.flat.device).wait_stream(self._comm)
+            if check_finite_on_host and not bool(torch.isfinite(self.flat).all()):
+                raise FloatingPointError("non-finite gradient after all-reduce")
             return
         for p in self.params:  # autograd may have re-pointed a grad (e.g. after set_to_none); restore the view
             if p.grad is None or p.grad.data_ptr() < self.flat.data_ptr() or \

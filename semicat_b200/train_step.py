@@ -275,6 +275,8 @@ _SIDE_STREAMS: dict = {}
 def _side_stream(device):
     if device not in _SIDE_STREAMS:
         _SIDE_STREAMS[device] = torch.cuda.Stream(device)
+        # a parameter's gradient now arrives from two streams; autograd synchronises them itself and only warns about it
+        torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
     return _SIDE_STREAMS[device]
 
 

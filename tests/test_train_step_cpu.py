@@ -54,7 +54,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fail_rank, out):
+def _worker(rank, world, port, fail_rank, out, buckets=0):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
     torch.set_num_threads(1)
@@ -63,6 +63,9 @@ def _worker(rank, world, port, fail_rank, out):
     try:
         net = _net()
         flat = ddp.FlatGradients(net.parameters())
+        if buckets:
+            assert flat.overlap_buckets(buckets) == buckets
+            flat.zero()
         x1, noise = _data(4)
         # each rank takes every world-th sample so that both ranks have a JVP part and a VFM part
         idx = torch.arange(rank, 4, world)
@@ -81,10 +84,10 @@ def _worker(rank, world, port, fail_rank, out):
             pass
 
 
-def _spawn(world, fail_rank=-1):
+def _spawn(world, fail_rank=-1, buckets=0):
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), fail_rank, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), fail_rank, out, buckets), nprocs=world, join=True)
     return dict(out)
 
 
@@ -103,6 +106,16 @@ def test_two_rank_gloo_allreduce_matches_single_process():
         total = total + _loss(net, x1[idx], {k: v[idx] for k, v in noise.items()}) / 2
     total.backward()
     assert torch.allclose(flat.flat, out[0], rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.timeout(180)
+def test_bucketed_allreduce_during_backward_gives_the_same_gradients():
+    """The exchange split into buckets that leave from autograd hooks while backward() is still running must end with
+    the same averaged gradients as one all-reduce after it."""
+    plain, bucketed = _spawn(2), _spawn(2, buckets=3)
+    assert all(torch.is_tensor(v) for v in bucketed.values()), bucketed
+    assert torch.equal(bucketed[0], bucketed[1])
+    assert torch.allclose(bucketed[0], plain[0], rtol=1e-6, atol=1e-8)
 
 
 @pytest.mark.timeout(180)
