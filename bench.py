@@ -563,6 +563,8 @@ def main():
                     help="training workloads: override the configuration's global batch (e.g. 64 = one rank's share of an 8-GPU run)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="training workloads: one stream for both branches of the objective and one all-reduce after the backward")
+    ap.add_argument("--kernel-mix", action="store_true",
+                    help="training workloads: profile one eager step and print the device time by kernel family and operator")
     ap.add_argument("--no-extras", action="store_true", help="skip the long-sequence point and the CPU baseline")
     ap.add_argument("--profile-mode", action="store_true",
                     help="for runs under ncu: eager launches (no CUDA graph), no end-to-end leg, no extras")
@@ -767,10 +769,73 @@ def main_sweep(args):
                       "peak": pk, "sweep": rows}))
 
 
+def kernel_mix(args):
+    """`--kernel-mix` with a training workload: one eager step under the torch profiler (after three warm-up steps), one
+    GPU; prints where the device time of the step goes, by kernel family and by operator.  Not a timing of the step (the
+    profiler serialises the launches); the timed numbers come from the plain run."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from semicat_b200 import _lib, train_step
+    _lib.load()
+    device = torch.device("cuda", 0)
+    tc = dict(TRAIN_CONFIGS[args.workload])
+    B = args.global_batch or tc["global_batch"]
+    torch.manual_seed(1234)
+    net = train_step.DiT(tc["vocab"], 768, 128, 12, 12, dropout=0.1, length=tc["length"], embed_type=tc["embed"]).to(device)
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-4, weight_decay=0.0, fused=True)
+    x1 = torch.randint(0, tc["vocab"], (B, tc["length"]), device=device)
+
+    def step():
+        noise = train_step.draw_noise(x1, tc["vocab"])
+        vf, sd = train_step.model_step(net, x1, noise, sd_prop=args.sd_prop, jvp_attention="jvp",
+                                       primal_attention=args.primal_attention, overlap_branches=not args.no_overlap)
+        opt.zero_grad(set_to_none=True)
+        train_step.total_loss(vf, sd).backward()
+        opt.step()
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        step()
+        torch.cuda.synchronize()
+    rows = prof.key_averages()
+    kernels = [r for r in rows if r.device_type.name == "CUDA"]
+    ops = [r for r in rows if r.device_type.name != "CUDA" and r.self_device_time_total > 0]
+
+    def family(name):
+        if "nvjet" in name or "gemm" in name.lower() or "cutlass" in name:
+            return "library GEMM"
+        if "jvpattn" in name:
+            return "this library: attention" if ("sm100_" in name or "row_dots" in name or "simt_" in name) else "this library: other"
+        if "Optimizer" in name or "multi_tensor" in name:
+            return "optimizer"
+        if "Memcpy" in name or "Memset" in name:
+            return "memcpy / memset"
+        return "PyTorch elementwise / reduction / copy"
+
+    fam = {}
+    for r in kernels:
+        if r.key.startswith("Optimizer.step"):
+            continue  # the profiler's own range around the optimizer, not a kernel
+        f = fam.setdefault(family(r.key), [0.0, 0])
+        f[0] += r.self_device_time_total
+        f[1] += r.count
+    total = sum(v[0] for v in fam.values())
+    print(json.dumps({
+        "workload": f"{args.workload}, batch {B} on one GPU, sd_prop {args.sd_prop}, one eager step under torch.profiler",
+        "device_ms_summed_over_kernels": total / 1e3, "kernels": sum(v[1] for v in fam.values()),
+        "by_family_ms": {k: {"ms": v[0] / 1e3, "launches": v[1]} for k, v in sorted(fam.items(), key=lambda kv: -kv[1][0])},
+        "top_operators_ms": [{"op": r.key, "ms": r.self_device_time_total / 1e3, "calls": r.count}
+                             for r in sorted(ops, key=lambda r: -r.self_device_time_total)[:30]]}))
+
+
 def main_train(args):
     """`--workload dit_lm1b | dit_text8`: the training step is the benchmark step; metric = tokens/s."""
     import torch
     from semicat_b200 import _lib, ddp
+    if args.kernel_mix:
+        return kernel_mix(args)
     _lib.load()
     rank, world, local_rank = ddp.init_from_env("nccl")
     torch.cuda.set_device(local_rank)
