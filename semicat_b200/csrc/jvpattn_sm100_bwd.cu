@@ -192,10 +192,11 @@ __global__ void __launch_bounds__(bwd_threads(bwd_parts(TILE))) sm100_bwd_kernel
   const int nx = (a.Lx + kRows - 1) / kRows;
   const int items = a.B * a.H * nx;
   auto decode = [&](int it, int &bb, int &hh, int &xx0) {
-    // The query owner walks the items from the back, the key owner from the front: each launch starts with the
-    // (batch, head) pairs that the launch before it (the forward front to back, then the query owner back to front)
-    // touched last, while their tensors are still in L2.
-    if (!kKV) it = items - 1 - it;
+    // Short sequences (a step's tensors are a few L2 sizes): the query owner walks the items from the back, the key
+    // owner from the front, so that each launch starts with the (batch, head) pairs that the launch before it (the
+    // forward front to back, then the query owner back to front) touched last, while their tensors are still in L2.
+    // At long sequences a launch outlives the cache many times over and the order is the plain one.
+    if (!kKV && ntiles <= 8) it = items - 1 - it;
     xx0 = (it % nx) * kRows;
     const int bh = it / nx;
     hh = bh % a.H;
