@@ -122,19 +122,21 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
 
 /* Caller-side helpers for the denoiser block around the attention (no counterpart among the reference's kernel wrappers;
  * they replace chains of PyTorch pointwise ops that, under torch.func.jvp, run as separate primal and tangent kernels):
- *   jvpattn_ln_modulate     h = LayerNorm(x) * (1 + scale) + shift      (semicat/net/duo.py:128-135, 159)
- *   jvpattn_gated_residual  z = x + mask * (gate * y)                   (duo.py:157, 160; mask = dropout keep / (1 - p) or NULL)
- * on (primal, tangent) pairs, with the VJPs of a cotangent on either output.  x, y, masks, outputs and gradients are
+ *   jvpattn_ln_modulate (+ jvpattn_ln_finalize)                 h = LayerNorm(x) * (1 + scale) + shift   (semicat/net/duo.py:128-135, 159)
+ *   jvpattn_gated_residual, jvpattn_gated_residual_dual         z = x + mask * (gate * y)                (duo.py:157, 160)
+ *   jvpattn_gelu_dual                                           the MLP's GELU                           (duo.py:118-123)
+ * on (primal, tangent) pairs, with the VJPs of cotangents on both outputs.  x, y, masks, outputs and gradients are
  * contiguous (batch, len, channels) tensors, shift / scale / gate are (batch, channels) views whose rows are `*_stride`
  * elements apart, gamma / beta are fp32 (channels); every other tensor has the one element type `dtype` (JVPATTN_BF16 or
- * JVPATTN_FP32).  channels must be 256, 512, 768 or 1024 (else JVPATTN_EINVAL: the caller keeps its PyTorch ops).
- * `which`: 0 forward (y; ln: also writes mean / rstd, fp32 (batch * len)), 1 forward of the tangent (ty from tx and the
- * tangents of the modulation; NULL tangents are zeros), 2 VJP of a cotangent `g` on y, 3 (ln only) VJP of a cotangent on ty.
- * The VJPs write the row-shaped gradients (ln: dx, dtx; gate: d1 = gradient of the gated branch, d2 = gradient of y through
- * the tangent output) and ADD per-sample column sums into `sums` (fp32, (3, batch, channels) for ln: sum_s g n, sum_s g,
- * sum_s g nd with n the normalised row and nd its tangent; (2, batch, channels) for gate: sum_s mask y g, sum_s mask ty g),
- * which the caller zeroes beforehand and turns into the gradients of shift / scale / gate / gamma / beta
- * (semicat_b200/dual_ops.py).  `exact` bit 0 selects the VJP of the LayerNorm tangent with respect to x: 0 reproduces PyTorch,
+ * JVPATTN_FP32).
+ *
+ * jvpattn_ln_modulate: channels must be 256, 512, 768 or 1024 (else JVPATTN_EINVAL: the caller keeps its PyTorch ops).
+ * `which`: 0 forward (y; also writes mean / rstd, fp32 (batch * len)), 1 forward of the tangent (ty from tx and the
+ * tangents of the modulation; NULL tangents are zeros), 2 VJP of a cotangent `g` on y (writes dx), 3 VJP of a cotangent on
+ * ty (writes dx and dtx).  The VJPs ADD per-sample column sums into `sums` (fp32; which = 2: (2, batch, channels) = sum_s g n,
+ * sum_s g with n the normalised row; which = 3: (3, batch, channels) = sum_s g n, sum_s g, sum_s g nd with nd the tangent of n),
+ * which the caller zeroes beforehand and hands to jvpattn_ln_finalize.  `exact` bit 0 selects the VJP of the LayerNorm
+ * tangent with respect to x: 0 reproduces PyTorch,
  * whose forward-mode formula for native_layer_norm treats the saved mean / rstd as constants when it is differentiated
  * again; 1 includes their dependence on x.  Bit 1 (which = 3 only): add to what dx holds instead of overwriting it, so that
  * the two backward kernels of one (primal, tangent) pair leave their sum. */
@@ -153,10 +155,11 @@ typedef struct jvpattn_dropout {
   float p;
 } jvpattn_dropout;
 
-int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
-                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int batch, int len, int channels, int dtype, const jvpattn_dropout *drop,
-                           void *stream);
+/* z = x + m gate y for the passes without a tangent (m = `mask`, or generated from `drop`, or all ones); gate: (batch,
+ * channels) rows `gate_stride` elements apart; channels a multiple of 8.  Its backward is jvpattn_gated_residual_dual
+ * (which = 1) with gtz = NULL. */
+int jvpattn_gated_residual(const void *x, const void *y, const void *gate, const void *mask, int64_t gate_stride, void *z,
+                           int batch, int len, int channels, int dtype, const jvpattn_dropout *drop, void *stream);
 
 /* Vocabulary-side head of the flow-map step (no counterpart among the reference's kernel wrappers; it replaces the softmax
  * over the vocabulary and the pointwise chain around it in semicat/models/semicat.py:210-229 and its forward-mode tangent,

@@ -133,7 +133,7 @@ def load() -> ctypes.CDLL:
         V, I64, I = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int
         lib.jvpattn_ln_modulate.argtypes = [I] + [V] * 8 + [I64, I64] + [V] * 7 + [I, I, I, ctypes.c_float, I, I, V]
         lib.jvpattn_ln_modulate.restype = ctypes.c_int
-        lib.jvpattn_gated_residual.argtypes = [I] + [V] * 6 + [I64, I64] + [V] * 5 + [I, I, I, I, ctypes.POINTER(Dropout), V]
+        lib.jvpattn_gated_residual.argtypes = [V] * 4 + [I64, V, I, I, I, I, ctypes.POINTER(Dropout), V]
         lib.jvpattn_gated_residual.restype = ctypes.c_int
         lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
         lib.jvpattn_flow_map_head.restype = ctypes.c_int

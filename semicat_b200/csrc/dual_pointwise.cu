@@ -1,17 +1,18 @@
 // Dual-number pointwise kernels for the denoiser block around the attention: every op takes a primal and a tangent and
-// returns both, and has hand-written VJPs for cotangents on either output.  Under torch.func.jvp the same algebra runs
-// as a dozen small kernels per op and per pass (primal and tangent separately), which is what bounds the training step
-// once the batch is sharded over several GPUs.
+// returns both in one pass, and has a hand-written VJP for the cotangents of both outputs.  Under torch.func.jvp the same
+// algebra runs as a dozen small kernels per op and per pass (primal and tangent separately), which is what bounds the
+// training step once the batch is sharded over several GPUs.
 //
 //   ln_modulate     h = LN(x) * (1 + scale) + shift        (semicat/net/duo.py:128-135, 159: LayerNorm + adaLN modulation)
 //   gated_residual  z = x + m * (g * y)                    (duo.py:157, 160: dropout(branch * gate) + skip; m = dropout keep
-//                                                           mask / (1 - p), all ones in evaluation)
+//                                                           mask / (1 - p): a tensor, or regenerated here from a seed)
+//   gelu_dual       the tanh-form GELU of the MLP          (duo.py:118-123)
 //
-// One warp owns one row of C channels (C = 256, 512, 768 or 1024; one element type, bf16 or fp32, for every tensor but
-// the fp32 LayerNorm weight and bias): 16-byte loads, fp32 arithmetic, warp-shuffle
-// row reductions.  Column sums that feed the gradients of per-sample or per-channel parameters are accumulated per CTA
-// (registers, then one shared-memory slice per warp) and added to fp32 [B, C] buffers with one atomic per column and
-// CTA (a CTA stays inside one sample).
+// LayerNorm: one warp owns one row of C channels (C = 256, 512, 768 or 1024; one element type, bf16 or fp32, for every
+// tensor but the fp32 LayerNorm weight and bias): 16-byte loads, fp32 arithmetic, warp-shuffle row reductions; column
+// sums that feed the gradients of per-sample or per-channel parameters are accumulated per CTA (registers, then one
+// shared-memory slice per warp) and added to fp32 [B, C] buffers with one atomic per column and CTA (a CTA stays inside
+// one sample); ln_finalize turns them into the parameter gradients.  Gated residual and GELU: 8 elements per thread.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -362,9 +363,6 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) ln_modulate_bwd_tangent_ker
   flush_column_sums<3, NV>(smem_raw, part, lane, dst);
 }
 
-// ---- gated residual.  z = x + m (g y)            tz = tx + m (g ty + tg y)
-// backward of z (cotangent G):   dx = G, dy = m g G, dg[b] += sum_s m y G
-// backward of tz (cotangent G):  dtx = G, dty = m g G, dtg[b] += sum_s m y G, dy = m tg G, dg[b] += sum_s m ty G
 // ---- dropout keep mask computed in the kernel instead of read from memory.  Philox-4x32-10 (Salmon et al., "Parallel
 // random numbers: as easy as 1, 2, 3", 2011) keyed by a 64-bit seed that lives in device memory (drawn once per training
 // step, so a replayed CUDA graph sees a new one), counter = (chunk index, call index): every kernel that touches the same
@@ -401,99 +399,34 @@ __device__ __forceinline__ void dropout8(const DropArgs &d, int64_t chunk, float
 }
 
 struct GateArgs {
-  const void *x, *y, *ty;    // [rows, C]; x may be null in the tangent forward without a tangent on x
-  const void *gate, *tgate;  // [B, C] rows `gate_stride` / `tgate_stride` apart (tgate may be null)
-  const void *mask;          // [rows, C] in the branch dtype: keep mask / (1 - p); null = all ones
-  int64_t gate_stride, tgate_stride;
-  void *z;                   // output
-  const void *g;             // cotangent
-  void *d1, *d2;             // backward outputs (see the kernels)
-  float *sums;               // [2, B, C]
+  const void *x, *y;         // [rows, C]
+  const void *gate;          // [B, C] rows `gate_stride` apart
+  const void *mask;          // [rows, C] in the branch dtype: keep mask / (1 - p); null = all ones (or generated, see drop)
+  int64_t gate_stride;
+  void *z;
   int B, S, C;
   DropArgs drop;             // used when mask is null and drop.seed is not
 };
 
-// mode 0: z = x + m g y.   mode 1: tz = tx + m (g ty + tg y)  (x = tx; either of tx / tg may be absent)
-template <typename T, int kMode>
+// z = x + m g y without a tangent (the passes that run outside forward-mode AD)
+template <typename T>
 __global__ void __launch_bounds__(256) gated_residual_fwd_kernel(GateArgs a) {
-  using XT = T;
-  using YT = T;
-  using MT = T;
   const int64_t total = (int64_t)a.B * a.S * a.C / 8;
   for (int64_t i8 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i8 < total; i8 += (int64_t)gridDim.x * blockDim.x) {
     const int64_t e = i8 * 8;
     const int c0 = (int)(e % a.C);
     const int b = (int)(e / ((int64_t)a.S * a.C));
     float xv[8], yv[8], gv[8], mv[8], out[8];
-    if (a.x) load8<XT>(static_cast<const XT *>(a.x) + e, xv);
-    load8<MT>(static_cast<const MT *>(a.gate) + (int64_t)b * a.gate_stride + c0, gv);
+    load8<T>(static_cast<const T *>(a.x) + e, xv);
+    load8<T>(static_cast<const T *>(a.y) + e, yv);
+    load8<T>(static_cast<const T *>(a.gate) + (int64_t)b * a.gate_stride + c0, gv);
     const bool masked = a.mask || a.drop.seed;
-    if (a.mask) load8<YT>(static_cast<const YT *>(a.mask) + e, mv);
+    if (a.mask) load8<T>(static_cast<const T *>(a.mask) + e, mv);
     else if (a.drop.seed) dropout8(a.drop, i8, mv);
-    if (kMode == 0) {
-      load8<YT>(static_cast<const YT *>(a.y) + e, yv);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) out[i] = (a.x ? xv[i] : 0.f) + (masked ? mv[i] : 1.f) * gv[i] * yv[i];
-    } else {
-      float tyv[8], tgv[8];
-      if (a.ty) load8<YT>(static_cast<const YT *>(a.ty) + e, tyv);
-      if (a.tgate) {
-        load8<YT>(static_cast<const YT *>(a.y) + e, yv);
-        load8<MT>(static_cast<const MT *>(a.tgate) + (int64_t)b * a.tgate_stride + c0, tgv);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float br = 0.f;
-        if (a.ty) br += gv[i] * tyv[i];
-        if (a.tgate) br += tgv[i] * yv[i];
-        out[i] = (a.x ? xv[i] : 0.f) + (masked ? mv[i] : 1.f) * br;
-      }
-    }
-    store8<XT>(static_cast<XT *>(a.z) + e, out);
+    for (int i = 0; i < 8; ++i) out[i] = xv[i] + (masked ? mv[i] : 1.f) * gv[i] * yv[i];
+    store8<T>(static_cast<T *>(a.z) + e, out);
   }
-}
-
-// Backward: d1 = m gate G  (gradient of the branch that `gate` multiplies), sums[0][b] += sum_s m y G (gradient of
-// that gate); with `tgate`: d2 = m tgate G (gradient of y through the tangent output), and with `ty`:
-// sums[1][b] += sum_s m ty G (gradient of gate through the tangent output).  The skip gradient is G itself.
-template <typename T, int NV>
-__global__ void __launch_bounds__(kWarpsPerCta * 32) gated_residual_bwd_kernel(GateArgs a, int rows_per_cta) {
-  extern __shared__ float smem_raw[];
-  constexpr int C = NV * 256;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int ctas_per_sample = (a.S + rows_per_cta - 1) / rows_per_cta;
-  const int b = blockIdx.x / ctas_per_sample;
-  const int s0 = (blockIdx.x % ctas_per_sample) * rows_per_cta;
-  const T *gate = static_cast<const T *>(a.gate) + (int64_t)b * a.gate_stride;
-  const T *tgate = a.tgate ? static_cast<const T *>(a.tgate) + (int64_t)b * a.tgate_stride : nullptr;
-  float part[2][NV][8] = {};
-  for (int r = warp; r < rows_per_cta && s0 + r < a.S; r += kWarpsPerCta) {
-    const int64_t off = ((int64_t)b * a.S + s0 + r) * C;
-#pragma unroll
-    for (int v = 0; v < NV; ++v) {
-      const int c0 = chan(v, lane);
-      float gv[8], yv[8], tyv[8], mv[8], gt[8], tgt[8], o1[8], o2[8];
-      load8<T>(static_cast<const T *>(a.g) + off + c0, gv);
-      load8<T>(static_cast<const T *>(a.y) + off + c0, yv);
-      if (a.ty) load8<T>(static_cast<const T *>(a.ty) + off + c0, tyv);
-      if (a.mask) load8<T>(static_cast<const T *>(a.mask) + off + c0, mv);
-      else if (a.drop.seed) dropout8(a.drop, (off + c0) / 8, mv);
-      load8<T>(gate + c0, gt);
-      if (tgate) load8<T>(tgate + c0, tgt);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float mg = ((a.mask || a.drop.seed) ? mv[i] : 1.f) * gv[i];
-        o1[i] = mg * gt[i];
-        part[0][v][i] += mg * yv[i];
-        if (tgate) o2[i] = mg * tgt[i];
-        if (a.ty) part[1][v][i] += mg * tyv[i];
-      }
-      store8<T>(static_cast<T *>(a.d1) + off + c0, o1);
-      if (tgate && a.d2) store8<T>(static_cast<T *>(a.d2) + off + c0, o2);
-    }
-  }
-  float *const dst[2] = {a.sums + (int64_t)b * C, a.sums + ((int64_t)a.B + b) * C};
-  flush_column_sums<2, NV>(smem_raw, part, lane, dst);
 }
 
 // Rows of one sample that a CTA of the backward kernels walks before it adds its column sums to global memory.  Every CTA
@@ -757,29 +690,19 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
   });
 }
 
-cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
-                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int B, int S, int C, int dtype, const unsigned long long *drop_seed,
-                           unsigned drop_call, float drop_p, cudaStream_t stream) {
-  GateArgs a{x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, B, S, C, {drop_seed, drop_call, drop_p}};
-  const int64_t rows = (int64_t)B * S;
-  if (rows == 0) return cudaSuccess;
+cudaError_t gated_residual(const void *x, const void *y, const void *gate, const void *mask, int64_t gate_stride, void *z, int B,
+                           int S, int C, int dtype, const unsigned long long *drop_seed, unsigned drop_call, float drop_p,
+                           cudaStream_t stream) {
+  const int64_t total = (int64_t)B * S * C / 8;
+  if (total == 0) return cudaSuccess;
+  if (C % 8) return cudaErrorInvalidValue;
+  GateArgs a{x, y, gate, mask, gate_stride, z, B, S, C, {drop_seed, drop_call, drop_p}};
   LaunchScope scope(kIdDual, stream);
-  return dispatch(dtype, C, [&](auto t, auto nv) -> cudaError_t {
-    using T = decltype(t);
-    constexpr int NV = decltype(nv)::value;
-    if (which == 0 || which == 1) {
-      const int64_t total = rows * C / 8;
-      const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
-      if (which == 0) gated_residual_fwd_kernel<T, 0><<<grid, 256, 0, stream>>>(a);
-      else gated_residual_fwd_kernel<T, 1><<<grid, 256, 0, stream>>>(a);
-    } else {
-      const int rows_cta = rows_per_cta(B, S, 16);
-      const unsigned grid = (unsigned)(B * ((S + rows_cta - 1) / rows_cta));
-      gated_residual_bwd_kernel<T, NV><<<grid, kWarpsPerCta * 32, kWarpsPerCta * 2 * NV * 256 * 4, stream>>>(a, rows_cta);
-    }
-    return cudaGetLastError();
-  });
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+  if (dtype == JVPATTN_BF16) gated_residual_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(a);
+  else if (dtype == JVPATTN_FP32) gated_residual_fwd_kernel<float><<<grid, 256, 0, stream>>>(a);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
 }
 
 cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, const float *beta, const void *scale,

@@ -249,23 +249,20 @@ int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *g
                                dx, dtx, sums, batch, len, channels, eps, exact, dtype, static_cast<cudaStream_t>(stream)));
 }
 
-int jvpattn_gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
-                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int batch, int len, int channels, int dtype, const jvpattn_dropout *drop,
-                           void *stream) {
-  if (which < 0 || which > 2 || !dual_shape_ok(batch, len, channels)) return JVPATTN_EINVAL;
-  if (drop && (!drop->seed || !(drop->p >= 0.f) || !(drop->p < 1.f))) return JVPATTN_EINVAL;
+int jvpattn_gated_residual(const void *x, const void *y, const void *gate, const void *mask, int64_t gate_stride, void *z,
+                           int batch, int len, int channels, int dtype, const jvpattn_dropout *drop, void *stream) {
+  if (batch < 0 || len < 0 || channels < 8 || channels % 8) return JVPATTN_EINVAL;
   if (dtype != JVPATTN_BF16 && dtype != JVPATTN_FP32) return JVPATTN_EINVAL;
+  if (drop && (!drop->seed || !(drop->p >= 0.f) || !(drop->p < 1.f))) return JVPATTN_EINVAL;
   DeviceInfo *d = nullptr;
   if (int rc = current_device(&d)) return rc;
   if ((int64_t)batch * len == 0) return JVPATTN_OK;
-  if (!gate) return JVPATTN_EINVAL;
-  if ((which == 0 && (!y || !z)) || (which == 1 && (!z || (!ty && !tgate) || (tgate && !y))) ||
-      (which == 2 && (!g || !y || !d1 || !sums)))
-    return JVPATTN_EINVAL;
-  if (gate_stride % 8 || tgate_stride % 8) return JVPATTN_EALIGN;
-  return note_cuda(gated_residual(which, x, y, ty, gate, tgate, mask, gate_stride, tgate_stride, z, g, d1, d2, sums, batch, len,
-                                  channels, dtype, drop ? reinterpret_cast<const unsigned long long *>(drop->seed) : nullptr,
+  if (!x || !y || !gate || !z) return JVPATTN_EINVAL;
+  for (const void *p : {x, y, gate, mask, (const void *)z})
+    if (p && reinterpret_cast<uintptr_t>(p) % 16) return JVPATTN_EALIGN;
+  if (gate_stride % 8) return JVPATTN_EALIGN;
+  return note_cuda(gated_residual(x, y, gate, mask, gate_stride, z, batch, len, channels, dtype,
+                                  drop ? reinterpret_cast<const unsigned long long *>(drop->seed) : nullptr,
                                   drop ? drop->call : 0u, drop ? drop->p : 0.f, static_cast<cudaStream_t>(stream)));
 }
 

@@ -65,11 +65,9 @@ cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *g
                         const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
                         float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int B, int S, int C,
                         float eps, int exact, int dtype, cudaStream_t stream);
-cudaError_t gated_residual(int which, const void *x, const void *y, const void *ty, const void *gate, const void *tgate,
-                           const void *mask, int64_t gate_stride, int64_t tgate_stride, void *z, const void *g, void *d1,
-                           void *d2, float *sums, int B, int S, int C, int dtype, const unsigned long long *drop_seed,
-                           unsigned drop_call, float drop_p, cudaStream_t stream);
-
+cudaError_t gated_residual(const void *x, const void *y, const void *gate, const void *mask, int64_t gate_stride, void *z, int B,
+                           int S, int C, int dtype, const unsigned long long *drop_seed, unsigned drop_call, float drop_p,
+                           cudaStream_t stream);
 cudaError_t ln_finalize(const float *p, const float *t, const float *gamma, const float *beta, const void *scale,
                         const void *tscale, int64_t mod_stride, int64_t tmod_stride, void *d_shift, void *d_scale, void *d_tshift,
                         void *d_tscale, float *d_gamma, float *d_beta, int B, int C, int dtype, cudaStream_t stream);

@@ -99,6 +99,9 @@ class FlatGradients:
 
     def _accumulated(self, i: int):
         self._pending[i] -= 1
+        if self._pending[i] < 0:
+            raise RuntimeError("FlatGradients.overlap_buckets: a second backward() since the last zero(); buckets of the first "
+                               "one have already been exchanged (accumulate over micro-batches without overlap_buckets)")
         if self._pending[i] == 0 and self._active():
             self._send(i)
 

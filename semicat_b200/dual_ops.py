@@ -243,14 +243,12 @@ def _drop_struct(drop):
     return ctypes.byref(_lib.Dropout(seed.data_ptr(), call, p))
 
 
-def _gate_launch(which, x, y, ty, gate, tgate, mask, z, g, d1, d2, sums, drop=None):
+def _gate_launch(x, y, gate, mask, z, drop=None):
     B, S, C = y.shape
     gt, gt_stride = _rows(gate, B, C)
-    tg, tg_stride = _rows(tgate, B, C)
     lib = _lib.load()
     with torch.cuda.device(y.device):
-        rc = lib.jvpattn_gated_residual(which, _ptr(x), _ptr(y), _ptr(ty), _ptr(gt), _ptr(tg), _ptr(mask), gt_stride, tg_stride,
-                                        _ptr(z), _ptr(g), _ptr(d1), _ptr(d2), _ptr(sums), B, S, C, _CODES[y.dtype],
+        rc = lib.jvpattn_gated_residual(_ptr(x), _ptr(y), _ptr(gt), _ptr(mask), gt_stride, _ptr(z), B, S, C, _CODES[y.dtype],
                                         _drop_struct(drop), _stream(y))
     _lib.check(rc, "jvpattn_gated_residual")
 
@@ -307,7 +305,7 @@ class _GatedResidual(torch.autograd.Function):
     @staticmethod
     def forward(x, y, gate, mask, drop):
         z = torch.empty_like(y)
-        _gate_launch(0, x, y, None, gate, None, mask, z, None, None, None, None, drop)
+        _gate_launch(x, y, gate, mask, z, drop)
         return z
 
     @staticmethod
