@@ -346,6 +346,58 @@ def gated_residual(skip: torch.Tensor, branch: torch.Tensor, gate: torch.Tensor,
     return fwAD.make_dual(z, tz)
 
 
+# ----------------------------------------------------------------------------------------------- linear layer
+class _DualLinear(torch.autograd.Function):
+    """(x, tx, w, b) -> (x w^T + b, tx w^T) as one autograd node: two GEMMs forward; backward two GEMMs for dx / dtx, two
+    for dw (the second accumulating into the first through the GEMM's own epilogue) and one reduction for db - no
+    additions of partial gradients and none of the scalings PyTorch's forward-mode formula for ``addmm`` carries."""
+
+    @staticmethod
+    def forward(x, tx, w, b):
+        return F.linear(x, w, b), F.linear(tx, w)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        x, tx, w, b = inputs
+        ctx.save_for_backward(x, tx, w)
+        ctx.has_bias = b is not None
+        ctx.set_materialize_grads(False)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gy, gty):
+        x, tx, w = ctx.saved_tensors
+        need_x, need_tx, need_w, need_b = ctx.needs_input_grad
+        K, N = w.shape[1], w.shape[0]
+        dx = dtx = dw = db = None
+        if gy is not None:
+            g2 = gy.reshape(-1, N)
+            if need_x:
+                dx = (g2 @ w).view(x.shape)
+            if need_w:
+                dw = g2.t() @ x.reshape(-1, K)
+            if need_b and ctx.has_bias:
+                db = g2.sum(0)
+        if gty is not None:
+            t2 = gty.reshape(-1, N)
+            if need_tx:
+                dtx = (t2 @ w).view(tx.shape)
+            if need_w:
+                dw = t2.t() @ tx.reshape(-1, K) if dw is None else torch.addmm(dw, t2.t(), tx.reshape(-1, K))
+        return dx, dtx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``F.linear`` that keeps primal and tangent in one autograd node under forward-mode AD (weight and bias are
+    parameters and carry no tangent where this is used).  Falls back to ``F.linear`` when no tangent is attached or the
+    operands' dtypes differ (autocast then does its own casting)."""
+    xp, tx = fwAD.unpack_dual(x)
+    if tx is None or not x.is_cuda or xp.dtype != weight.dtype or (bias is not None and bias.dtype != weight.dtype):
+        return F.linear(x, weight, bias)
+    y, ty = _DualLinear.apply(xp, tx.to(xp.dtype), weight, bias)
+    return fwAD.make_dual(y, ty)
+
+
 # ----------------------------------------------------------------------------------------------- GELU (tanh form)
 def _gelu_launch(mode, h, v, w, u, out, out2):
     lib = _lib.load()

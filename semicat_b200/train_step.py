@@ -27,6 +27,7 @@ import torch.nn.functional as F
 
 from . import vocab_ops
 from .dual_ops import dropout_seed, flow_map_head, gated_residual, gelu_tanh, ln_modulate
+from .dual_ops import linear as dual_linear
 from .functional import safe_sdpa_jvp
 from .rotary import apply_rotary_cast
 
@@ -76,7 +77,7 @@ def _aligned_linear(x, lin: nn.Linear, in_scale: float = 1.0, keep_padding: bool
     w, b = prepared if prepared is not None else _prepare_aligned(lin, in_scale, dt if pad_in else None)
     if pad_in and x.shape[-1] != n_in + pad_in:
         x = F.pad(x.to(w.dtype), (0, pad_in))
-    y = F.linear(x, w, b)
+    y = dual_linear(x, w, b)
     return y[..., :n_out] if pad_out and not keep_padding else y
 
 
@@ -107,12 +108,14 @@ class Block(nn.Module):
 
     def forward(self, x, cos, sin, c, attention):
         B, S, _ = x.shape
-        sh1, sc1, g1, sh2, sc2, g2 = self.ada(c)[:, None].chunk(6, dim=2)
         # On the GPU the pointwise chain around the attention runs as fused (primal, tangent) kernels (dual_ops); the
         # plain-formula path ("math") keeps the PyTorch expressions and serves as the independent check.
         fused = x.is_cuda and attention != "math"
+        mod = dual_linear(c, self.ada.weight, self.ada.bias) if fused else self.ada(c)
+        sh1, sc1, g1, sh2, sc2, g2 = mod[:, None].chunk(6, dim=2)
         h = ln_modulate(x, self.norm1, sh1, sc1) if fused else self.norm1(x) * (1.0 + sc1) + sh1
-        q, k, v = self.attn_qkv(h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
+        lin = (lambda m, z: dual_linear(z, m.weight, m.bias)) if fused else (lambda m, z: m(z))
+        q, k, v = lin(self.attn_qkv, h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
         if x.is_cuda and attention != "math":
             # one kernel per tensor (and per tangent) instead of the fp32 pointwise chain plus the casts to bf16
             rot_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
@@ -131,8 +134,8 @@ class Block(nn.Module):
         else:
             a = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2).to(q.dtype)).transpose(1, 2)
         if fused:
-            x = gated_residual(x, self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)), g1, self.drop.p, self.training)
-            m = self.mlp[2](gelu_tanh(self.mlp[0](ln_modulate(x, self.norm2, sh2, sc2))))
+            x = gated_residual(x, lin(self.attn_out, a.reshape(B, S, self.dim).to(h.dtype)), g1, self.drop.p, self.training)
+            m = lin(self.mlp[2], gelu_tanh(lin(self.mlp[0], ln_modulate(x, self.norm2, sh2, sc2))))
             return gated_residual(x, m, g2, self.drop.p, self.training)
         x = self.drop(self.attn_out(a.reshape(B, S, self.dim).to(h.dtype)) * g1) + x
         return self.drop(self.mlp(self.norm2(x) * (1.0 + sc2) + sh2) * g2) + x
@@ -194,8 +197,11 @@ class DiT(nn.Module):
         h = self.embed(x, s, cond)
         for blk in self.blocks:
             h = blk(h, self.cos, self.sin, cond, attention)
-        shift, scale = self.ada_out(cond)[:, None].chunk(2, dim=2)
-        return _aligned_linear(self.norm_out(h) * (1.0 + scale) + shift, self.head, keep_padding=padded_logits)
+        fused = h.is_cuda and attention != "math"
+        mod = dual_linear(cond, self.ada_out.weight, self.ada_out.bias) if fused else self.ada_out(cond)
+        shift, scale = mod[:, None].chunk(2, dim=2)
+        out = ln_modulate(h, self.norm_out, shift, scale) if fused else self.norm_out(h) * (1.0 + scale) + shift
+        return _aligned_linear(out, self.head, keep_padding=padded_logits)
 
 
 _REFERENCE_NAMES = (  # prefix in semicat/net/duo.py's DIT -> prefix here
