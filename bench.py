@@ -330,16 +330,31 @@ def run_train(name, steps, warmup, device, rank, world, dist, sampler, sd_prop=0
     loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
     x1 = torch.empty(hi - lo, tc["length"], dtype=torch.long, device=device)
 
+    # The noise of step i + 1 is drawn while step i is still running: the last kernel that reads the noise is the first
+    # node of the backward (the self-distillation loss), after which a second stream refills the buffers in place under
+    # the rest of the backward (an 8 GB write at the lm1b shape, hidden under GEMMs that do not use the memory system).
+    noise = train_step.draw_noise(x1, tc["vocab"])
+    noise_stream = torch.cuda.Stream(device) if overlap else None
+
+    def refill():
+        if noise_stream is None:
+            train_step.draw_noise(x1, tc["vocab"], out=noise)
+            return
+        noise_stream.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(noise_stream):
+            train_step.draw_noise(x1, tc["vocab"], out=noise)
+
     def body():
-        noise = train_step.draw_noise(x1, tc["vocab"])
         flat.zero()
         vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention=attention,
-                                       primal_attention=primal_attention, overlap_branches=overlap)
+                                       primal_attention=primal_attention, overlap_branches=overlap, noise_released=refill)
         loss = train_step.total_loss(vf, sd)
         loss.backward()
         flat.all_reduce_mean()
         opt.step()
         loss_host.copy_(loss.detach(), non_blocking=True)
+        if noise_stream is not None:
+            torch.cuda.current_stream(device).wait_stream(noise_stream)
 
     graph = None
 

@@ -257,14 +257,22 @@ def flow_map(net, x, s, t, attention):
     return x + dt.view(-1, 1, 1) * diff
 
 
-def draw_noise(x1, vocab, generator=None):
+def draw_noise(x1, vocab, generator=None, out=None):
     """The random draws of one step, separated out so that tests can inject the same draws everywhere.  On the GPU the
     noise rows are spaced a multiple of 8 columns apart (16-byte aligned rows for the fused vocabulary-side kernels);
-    ``x0`` is the (B, L, vocab) view of that buffer."""
+    ``x0`` is the (B, L, vocab) view of that buffer.  With ``out`` (a dict this function returned) the same buffers are
+    refilled in place, which lets a training loop draw the next step's noise while the current step is still running
+    (see ``model_step(noise_released=...)``)."""
     B = x1.shape[0]
     dev = x1.device
+    if out is not None:
+        out["x0_buffer"].normal_(generator=generator)
+        for k in ("t_vfm", "t_sd", "u_sd"):
+            out[k].uniform_(generator=generator)
+        return out
     width = vocab_ops.padded(vocab) if dev.type == "cuda" else vocab
-    return {"x0": torch.randn(B, x1.shape[1], width, device=dev, generator=generator)[..., :vocab],
+    buf = torch.randn(B, x1.shape[1], width, device=dev, generator=generator)
+    return {"x0": buf[..., :vocab], "x0_buffer": buf,
             "t_vfm": torch.rand(B, device=dev, generator=generator), "t_sd": torch.rand(B, device=dev, generator=generator),
             "u_sd": torch.rand(B, device=dev, generator=generator)}
 
@@ -286,7 +294,8 @@ def _side_stream(device):
     return _SIDE_STREAMS[device]
 
 
-def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dtype, label_smoothing, overlap=True):
+def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dtype, label_smoothing, overlap=True,
+                      noise_released=None):
     """``model_step`` with the (B, L, V) tensors kept in one 16-bit padded layout between the noise and the two scalar
     losses (vocab_ops): same objective, same rounding points at the network's boundary (input and logits in ``dtype``).
 
@@ -318,6 +327,12 @@ def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dt
         with torch.no_grad():
             target = net(xst, t, t, attention=primal_attention, padded_logits=True)
         sd_loss = vocab_ops.sd_lag_loss(logits, tlogits, target, x0[:split], x1[:split], s, t, lse)
+        if noise_released is not None:
+            # the last reader of the noise is the backward kernel of this loss, the first node of the reverse pass: the
+            # gradient of the logits exists as soon as it has been enqueued
+            logits.register_hook(lambda _g: noise_released())
+    elif noise_released is not None:
+        noise_released()
     main.wait_stream(side)
     return vf_loss, sd_loss
 
@@ -356,11 +371,15 @@ class _StepCasts:
 
 
 def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype=torch.bfloat16, label_smoothing=0.0,
-               primal_attention="sdpa", overlap_branches=True):
+               primal_attention="sdpa", overlap_branches=True, noise_released=None):
     """One training objective evaluation: returns (vfm_loss, sd_loss or None).  ``x1`` are token ids (B, L).
     ``jvp_attention`` selects the attention of the forward-mode pass, ``primal_attention`` that of the passes without
     tangents (the cross-entropy step and the no-grad target): "sdpa" is ``F.scaled_dot_product_attention`` as in the
-    reference (semicat/net/duo.py:143-152), "lib" this library's primal-only kernels, "math" the plain formula."""
+    reference (semicat/net/duo.py:143-152), "lib" this library's primal-only kernels, "math" the plain formula.
+    ``noise_released``: optional callable, invoked on the host as soon as the last kernel that reads ``noise`` has been
+    enqueued (during ``backward()`` when the self-distillation loss reads the noise again, else before this returns); the
+    stream that is current at that moment is the one the reader was enqueued on.  A training loop uses it to refill the
+    noise buffers for the next step on another stream under the rest of the backward."""
     B = x1.shape[0]
     split = int(sd_prop * B)
     dev_type = x1.device.type
@@ -374,12 +393,13 @@ def model_step(net, x1, noise, sd_prop=0.25, jvp_attention="jvp", autocast_dtype
     try:
         with seeded:
             return _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention,
-                               overlap_branches)
+                               overlap_branches, noise_released)
     finally:
         net.close()
 
 
-def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention, overlap_branches):
+def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, label_smoothing, primal_attention, overlap_branches,
+                noise_released=None):
     B = x1.shape[0]
     dev_type = x1.device.type
     x0 = noise["x0"]
@@ -387,7 +407,7 @@ def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, lab
         io_dtype = autocast_dtype if autocast_dtype is not None else torch.float32
         if _fused_vocabulary_side(model, x0, jvp_attention, io_dtype) and primal_attention != "math":
             return _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, io_dtype, label_smoothing,
-                                     overlap_branches)
+                                     overlap_branches, noise_released)
         # VFM step on the tail of the batch
         vf_loss = None
         if split < B:
@@ -399,6 +419,8 @@ def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, lab
             # in the transposed (B, V, L) layout it is a strided "spatial" softmax that took a third of the whole step.
             vf_loss = F.cross_entropy(pred.float().reshape(-1, pred.shape[-1]), x1[split:].reshape(-1), label_smoothing=label_smoothing)
         if split == 0:
+            if noise_released is not None:
+                noise_released()
             return vf_loss, None
         # self-distillation ("lag") step on the head of the batch: d/dt of the flow map by forward-mode AD
         t = noise["t_sd"][:split]
@@ -409,6 +431,8 @@ def _model_step(model, net, x1, noise, split, jvp_attention, autocast_dtype, lab
         with torch.no_grad():
             target = net(xst, t, t, attention=primal_attention).softmax(dim=-1)
     sd_loss = ((1.0 - t).view(-1, 1, 1) * dv - target + xst).pow(2).sum(dim=-1).mean()
+    if noise_released is not None:
+        noise_released()  # this path reads the noise in the forward only (the interpolated inputs are tensors of their own)
     return vf_loss, sd_loss
 
 
