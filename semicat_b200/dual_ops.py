@@ -185,15 +185,11 @@ class _LnModulate(torch.autograd.Function):
         x, gamma, beta, shift, scale, mean, rstd = ctx.saved_tensors
         B, S, C = x.shape
         dx = torch.empty_like(x)
-        sums = torch.zeros(2, B, C, dtype=torch.float32, device=x.device)
+        zeros = torch.zeros(2 * B * C + 2 * C, dtype=torch.float32, device=x.device)
+        sums, param_grads = zeros[:2 * B * C].view(2, B, C), zeros[2 * B * C:].view(2, C)
         _ln_launch(2, x, None, gamma, None, None, scale, None, None, mean, rstd, None, g.contiguous(), dx, None, sums, ctx.eps, ctx.exact)
-        gn, g1 = sums[0], sums[1]
-        sc1 = 1.0 + scale.reshape(B, C).float()
-        d_shift = g1.to(shift.dtype).reshape(shift.shape)
-        d_scale = (gamma * gn + (beta * g1 if beta is not None else 0.0)).to(scale.dtype).reshape(scale.shape)
-        d_gamma = (gn * sc1).sum(0)
-        d_beta = (g1 * sc1).sum(0) if beta is not None else None
-        return dx, d_gamma, d_beta, d_shift, d_scale, None, None
+        d_shift, d_scale, _, _, d_gamma, d_beta = _ln_finalize(sums, None, gamma, beta, scale, None, (False, False), B, C, param_grads)
+        return dx, d_gamma, d_beta, d_shift.reshape(shift.shape), d_scale.reshape(scale.shape), None, None
 
 
 def ln_modulate(x: torch.Tensor, norm: torch.nn.LayerNorm, shift: torch.Tensor, scale: torch.Tensor, exact: bool = False) -> torch.Tensor:
