@@ -337,11 +337,43 @@ def _model_step_fused(net, x1, noise, split, jvp_attention, primal_attention, dt
     return vf_loss, sd_loss
 
 
+class _CastParams(torch.autograd.Function):
+    """All 16-bit copies of a step in one node: the casts run as a few multi-tensor launches into one flat buffer instead of
+    one kernel per parameter, and so do the casts of their gradients back to fp32 in the backward."""
+
+    @staticmethod
+    def forward(ctx, dtype, *params):
+        flat = torch.empty(sum(p.numel() for p in params), dtype=dtype, device=params[0].device)
+        outs, off = [], 0
+        for p in params:
+            outs.append(flat[off:off + p.numel()].view(p.shape))
+            off += p.numel()
+        torch._foreach_copy_(outs, [p.detach() for p in params])
+        ctx.shapes = [p.shape for p in params]
+        ctx.param_dtype = params[0].dtype
+        return tuple(outs)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, *grads):
+        live = [i for i, g in enumerate(grads) if g is not None]
+        if not live:
+            return (None,) * (1 + len(grads))
+        flat = torch.empty(sum(grads[i].numel() for i in live), dtype=ctx.param_dtype, device=grads[live[0]].device)
+        outs, off = [None] * len(grads), 0
+        for i in live:
+            n = grads[i].numel()
+            outs[i] = flat[off:off + n].view(ctx.shapes[i])
+            off += n
+        torch._foreach_copy_([outs[i] for i in live], [grads[i] for i in live])
+        return (None, *outs)
+
+
 class _StepCasts:
     """The 16-bit copies of the ``nn.Linear`` parameters for one objective evaluation, made once and shared by its three
     passes.  Autocast keeps such a cache itself, but not inside ``torch.func.jvp`` (wrapped tensors are not leaves), where
-    every use of a weight was cast again: five casts per parameter and step.  The casts are ordinary differentiable ops, so
-    a weight's gradients from the passes are summed in 16 bits and cast back to fp32 once."""
+    every use of a weight was cast again: five casts per parameter and step.  The casts are one differentiable node
+    (``_CastParams``), so a weight's gradients from the passes are summed in 16 bits and cast back to fp32 once."""
 
     def __init__(self, net, dtype):
         self.net, self.params, self.aligned = net, {}, []
@@ -350,6 +382,7 @@ class _StepCasts:
         vocab_sized = {id(net.head): 1.0}
         if isinstance(net.embed, NaiveEmbed):
             vocab_sized[id(net.embed.seq)] = 1.0 / net.embed.coeff
+        names, tensors = [], []
         for mname, m in net.named_modules():
             if not isinstance(m, nn.Linear):
                 continue
@@ -358,7 +391,17 @@ class _StepCasts:
                 self.aligned.append(m)
             else:
                 for pname, p in m.named_parameters(recurse=False):
-                    self.params[f"{mname}.{pname}"] = p.to(dtype)
+                    names.append(f"{mname}.{pname}")
+                    tensors.append(p)
+        # A few nodes rather than one: a node's backward runs when the gradients of ALL its outputs exist, and a
+        # data-parallel caller wants the late layers' gradients early (to exchange them under the rest of the backward).
+        total, groups, start, acc = sum(t.numel() for t in tensors), 4, 0, 0
+        for i, t in enumerate(tensors):
+            acc += t.numel()
+            if acc >= total / groups or i == len(tensors) - 1:
+                cast = _CastParams.apply(dtype, *tensors[start:i + 1])
+                self.params.update(zip(names[start:i + 1], cast))
+                start, acc = i + 1, 0
 
     def __call__(self, *args, **kwargs):
         if not self.params:
