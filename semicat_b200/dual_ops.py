@@ -2,11 +2,12 @@
 
 Callers of ``safe_sdpa_jvp`` run the whole block under ``torch.func.jvp`` (semicat/models/semicat.py:153-157), where
 every pointwise op of semicat/net/duo.py:127-166 becomes several small kernels for the primal and several more for the
-tangent, and again for each of them in the backward.  Three ops cover most of that chain:
+tangent, and again for each of them in the backward.  Four ops cover most of that chain:
 
 * :func:`ln_modulate` - ``norm(x) * (1 + scale) + shift`` (duo.py:128-135 and :159),
 * :func:`gated_residual` - ``dropout(branch * gate) + skip`` (duo.py:157 and :160),
-* :func:`gelu_tanh` - the GELU of the block's MLP (duo.py:118-123).
+* :func:`gelu_tanh` - the GELU of the block's MLP (duo.py:118-123),
+* :func:`linear` - ``F.linear`` with primal and tangent in one node (the GEMMs stay the BLAS library's).
 
 Under forward-mode AD each op unpacks its dual inputs (``torch.autograd.forward_ad.unpack_dual``), runs ONE
 ``torch.autograd.Function`` that maps primals and tangents to (output, output tangent), and packs the pair into a dual
