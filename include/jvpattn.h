@@ -120,6 +120,17 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
                         const float *cos, const float *sin, int batch, int len, int heads, int head_dim, int transpose,
                         void *stream);
 
+/* jvpattn_rotary_cast for q, k and v of one projection in one launch: three (input view, output view) pairs of shape
+ * (batch, len, heads, head_dim) with unit channel stride; pairs 0 and 1 are rotated (transpose as above), pair 2 is
+ * copied (and cast).  in_strides / out_strides: element strides of (batch, position, head) for each pair, 3 x 3 values;
+ * every pointer 16-byte aligned, every stride a multiple of 8 (else JVPATTN_EALIGN).  Forward: the three inputs are the
+ * slices of the block's (batch, len, 3, heads, head_dim) projection, the outputs three contiguous tensors; backward
+ * (transpose = 1): the inputs are the three gradients and the outputs the slices of the projection's gradient, which is
+ * thereby written in place (semicat/net/duo.py:137-141).  Dtypes: JVPATTN_BF16 or JVPATTN_FP32 on either side. */
+int jvpattn_rotary_qkv(const void *const in[3], const int64_t in_strides[9], int in_dtype, void *const out[3],
+                       const int64_t out_strides[9], int out_dtype, const float *cos, const float *sin, int batch, int len,
+                       int heads, int head_dim, int transpose, void *stream);
+
 /* Caller-side helpers for the denoiser block around the attention (no counterpart among the reference's kernel wrappers;
  * they replace chains of PyTorch pointwise ops that, under torch.func.jvp, run as separate primal and tangent kernels):
  *   jvpattn_ln_modulate (+ jvpattn_ln_finalize)                 h = LayerNorm(x) * (1 + scale) + shift   (semicat/net/duo.py:128-135, 159)

@@ -31,7 +31,7 @@ EXPORTS = (
     "jvpattn_abi_version", "jvpattn_profile_begin", "jvpattn_profile_end", "jvpattn_kernel_name",
     "jvpattn_bwd_static", "jvpattn_rotary_cast", "jvpattn_stream_check", "jvpattn_debug_set",
     "jvpattn_ln_modulate", "jvpattn_gated_residual", "jvpattn_flow_map_head", "jvpattn_gelu_dual", "jvpattn_vocab_op",
-    "jvpattn_gated_residual_dual", "jvpattn_ln_finalize",
+    "jvpattn_gated_residual_dual", "jvpattn_ln_finalize", "jvpattn_rotary_qkv",
 )
 DEBUG_WAIT_CYCLES, DEBUG_STALL_NEXT_FWD = 0, 1
 STATIC_SCRATCH_ROWS = 262144
@@ -137,6 +137,9 @@ def load() -> ctypes.CDLL:
         lib.jvpattn_gated_residual.restype = ctypes.c_int
         lib.jvpattn_flow_map_head.argtypes = [I, V, V, I64, I64] + [V] * 8 + [I, I, I, I, V]
         lib.jvpattn_flow_map_head.restype = ctypes.c_int
+        P3, S9 = ctypes.POINTER(ctypes.c_void_p * 3), ctypes.POINTER(ctypes.c_int64 * 9)
+        lib.jvpattn_rotary_qkv.argtypes = [P3, S9, I, P3, S9, I, V, V, I, I, I, I, I, V]
+        lib.jvpattn_rotary_qkv.restype = ctypes.c_int
         lib.jvpattn_gelu_dual.argtypes = [I] + [V] * 6 + [I64, I, V]
         lib.jvpattn_gated_residual_dual.argtypes = [I] + [V] * 7 + [I64, I64] + [V] * 7 + [I, I, I, I, ctypes.POINTER(Dropout), V]
         lib.jvpattn_gated_residual_dual.restype = ctypes.c_int

@@ -231,6 +231,27 @@ int jvpattn_rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
                                static_cast<cudaStream_t>(stream)));
 }
 
+int jvpattn_rotary_qkv(const void *const in[3], const int64_t in_strides[9], int in_dtype, void *const out[3],
+                       const int64_t out_strides[9], int out_dtype, const float *cosv, const float *sinv, int batch, int len,
+                       int heads, int head_dim, int transpose, void *stream) {
+  if (batch < 0 || len < 0 || heads < 0 || head_dim < 16 || head_dim % 16 != 0) return JVPATTN_EINVAL;
+  if ((in_dtype != JVPATTN_BF16 && in_dtype != JVPATTN_FP32) || (out_dtype != JVPATTN_BF16 && out_dtype != JVPATTN_FP32))
+    return JVPATTN_EINVAL;
+  DeviceInfo *d = nullptr;
+  if (int rc = current_device(&d)) return rc;
+  if ((int64_t)batch * len * heads == 0) return JVPATTN_OK;
+  if (!in || !out || !in_strides || !out_strides || !cosv || !sinv) return JVPATTN_EINVAL;
+  if (reinterpret_cast<uintptr_t>(cosv) % 16 || reinterpret_cast<uintptr_t>(sinv) % 16) return JVPATTN_EALIGN;
+  for (int t = 0; t < 3; ++t) {
+    if (!in[t] || !out[t]) return JVPATTN_EINVAL;
+    if (reinterpret_cast<uintptr_t>(in[t]) % 16 || reinterpret_cast<uintptr_t>(out[t]) % 16) return JVPATTN_EALIGN;
+    for (int k = 0; k < 3; ++k)
+      if (in_strides[3 * t + k] % 8 || out_strides[3 * t + k] % 8) return JVPATTN_EALIGN;
+  }
+  return note_cuda(rotary_qkv(in, in_strides, in_dtype, out, out_strides, out_dtype, cosv, sinv, batch, len, heads, head_dim,
+                              transpose, static_cast<cudaStream_t>(stream)));
+}
+
 int jvpattn_ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,
                         const void *scale, const void *tshift, const void *tscale, int64_t mod_stride, int64_t tmod_stride,
                         float *mean, float *rstd, void *out, const void *g, void *dx, void *dtx, float *sums, int batch, int len,

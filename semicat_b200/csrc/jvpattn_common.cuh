@@ -59,6 +59,10 @@ size_t sm100_bwd_workspace_bytes(int B, int H, int Lq, int Lk, int D, int stat_l
 cudaError_t rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int in_dtype, void *y, int out_dtype,
                         const float *cosv, const float *sinv, int B, int S, int H, int D, int transpose, cudaStream_t stream);
 
+cudaError_t rotary_qkv(const void *const in[3], const int64_t in_strides[9], int in_dtype, void *const out[3],
+                       const int64_t out_strides[9], int out_dtype, const float *cosv, const float *sinv, int B, int S, int H, int D,
+                       int transpose, cudaStream_t stream);
+
 // dual_pointwise.cu: LayerNorm + modulation and gated residual on (primal, tangent) pairs, with their VJPs
 bool dual_shape_ok(int B, int S, int C);
 cudaError_t ln_modulate(int which, const void *x, const void *tx, const float *gamma, const float *beta, const void *shift,

@@ -133,6 +133,68 @@ cudaError_t launch(const void *x, int64_t sb, int64_t ss, int64_t sh, void *y, c
   return cudaGetLastError();
 }
 
+// ---- q, k and v of one projection in one launch.  The block splits its qkv projection (B, S, 3, H, D) into three
+// (B, S, H, D) tensors, rotates two of them and hands all three to the attention; in the backward the three gradients
+// have to come back as one (B, S, 3, H, D) tensor.  With one kernel over three (input view, output view) pairs - rotation
+// for the first two, a plain copy for the third - the forward is one launch instead of two plus a strided read, and the
+// backward writes the projection's gradient in place instead of three tensors that PyTorch then concatenates.
+struct QkvArgs {
+  const void *in[3];
+  void *out[3];
+  int64_t isb[3], iss[3], ish[3], osb[3], oss[3], osh[3];  // element strides of (batch, position, head); channels are unit
+  const float *cosv, *sinv;
+  int B, S, H, D, transpose;
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256) rotary_qkv_kernel(QkvArgs a) {
+  const int half = a.D / 2, per_row = half / 8;
+  const int64_t rows = (int64_t)a.B * a.S * a.H;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t rr = gid / per_row;
+  if (rr >= 3 * rows) return;
+  const int t = (int)(rr / rows);
+  const int64_t r = rr % rows;
+  const int c0 = (int)(gid % per_row) * 8;
+  const int h = (int)(r % a.H);
+  const int s = (int)((r / a.H) % a.S);
+  const int b = (int)(r / ((int64_t)a.H * a.S));
+  const TI *xr = static_cast<const TI *>(a.in[t]) + b * a.isb[t] + s * a.iss[t] + h * a.ish[t];
+  TO *yr = static_cast<TO *>(a.out[t]) + b * a.osb[t] + s * a.oss[t] + h * a.osh[t];
+  float x1[8], x2[8], y1[8], y2[8];
+  Vec8<TI>::load(xr + c0, x1);
+  Vec8<TI>::load(xr + half + c0, x2);
+  if (t < 2) {
+    float c[8], sn[8];
+    Vec8<float>::load(a.cosv + (int64_t)s * half + c0, c);
+    Vec8<float>::load(a.sinv + (int64_t)s * half + c0, sn);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (a.transpose) {
+        y1[i] = __fadd_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i]));
+        y2[i] = __fsub_rn(__fmul_rn(x2[i], c[i]), __fmul_rn(x1[i], sn[i]));
+      } else {
+        y1[i] = __fsub_rn(__fmul_rn(x1[i], c[i]), __fmul_rn(x2[i], sn[i]));
+        y2[i] = __fadd_rn(__fmul_rn(x1[i], sn[i]), __fmul_rn(x2[i], c[i]));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y1[i] = x1[i], y2[i] = x2[i];
+  }
+  Vec8<TO>::store(yr + c0, y1);
+  Vec8<TO>::store(yr + half + c0, y2);
+}
+
+template <typename TI, typename TO>
+cudaError_t launch_qkv(const QkvArgs &a, cudaStream_t stream) {
+  const int64_t threads = (int64_t)3 * a.B * a.S * a.H * (a.D / 16);
+  if (threads == 0) return cudaSuccess;
+  LaunchScope scope(kIdRotary, stream);
+  rotary_qkv_kernel<TI, TO><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 // dtype codes: 0 bf16, 1 fp16, 2 fp32 (include/jvpattn.h)
@@ -152,6 +214,28 @@ cudaError_t rotary_cast(const void *x, int64_t sb, int64_t ss, int64_t sh, int i
     default: return cudaErrorInvalidValue;
   }
 #undef JVP_ROT
+}
+
+cudaError_t rotary_qkv(const void *const in[3], const int64_t in_strides[9], int in_dtype, void *const out[3],
+                       const int64_t out_strides[9], int out_dtype, const float *cosv, const float *sinv, int B, int S, int H, int D,
+                       int transpose, cudaStream_t stream) {
+  QkvArgs a{};
+  for (int t = 0; t < 3; ++t) {
+    a.in[t] = in[t];
+    a.out[t] = out[t];
+    a.isb[t] = in_strides[3 * t], a.iss[t] = in_strides[3 * t + 1], a.ish[t] = in_strides[3 * t + 2];
+    a.osb[t] = out_strides[3 * t], a.oss[t] = out_strides[3 * t + 1], a.osh[t] = out_strides[3 * t + 2];
+  }
+  a.cosv = cosv, a.sinv = sinv, a.B = B, a.S = S, a.H = H, a.D = D, a.transpose = transpose;
+#define JVP_QKV(TI, TO) return launch_qkv<TI, TO>(a, stream)
+  switch (in_dtype * 3 + out_dtype) {
+    case 0: JVP_QKV(__nv_bfloat16, __nv_bfloat16);
+    case 2: JVP_QKV(__nv_bfloat16, float);
+    case 6: JVP_QKV(float, __nv_bfloat16);
+    case 8: JVP_QKV(float, float);
+    default: return cudaErrorInvalidValue;
+  }
+#undef JVP_QKV
 }
 
 }  // namespace jvpattn

@@ -29,7 +29,7 @@ from . import vocab_ops
 from .dual_ops import dropout_seed, flow_map_head, gated_residual, gelu_tanh, ln_modulate
 from .dual_ops import linear as dual_linear
 from .functional import safe_sdpa_jvp
-from .rotary import apply_rotary_cast
+from .rotary import apply_rotary_cast, rotary_qkv
 
 
 def _rotate(x, cos, sin):
@@ -115,13 +115,14 @@ class Block(nn.Module):
         sh1, sc1, g1, sh2, sc2, g2 = mod[:, None].chunk(6, dim=2)
         h = ln_modulate(x, self.norm1, sh1, sc1) if fused else self.norm1(x) * (1.0 + sc1) + sh1
         lin = (lambda m, z: dual_linear(z, m.weight, m.bias)) if fused else (lambda m, z: m(z))
-        q, k, v = lin(self.attn_qkv, h).reshape(B, S, 3, self.heads, self.dim // self.heads).unbind(2)
+        qkv = lin(self.attn_qkv, h).reshape(B, S, 3, self.heads, self.dim // self.heads)
         if x.is_cuda and attention != "math":
-            # one kernel per tensor (and per tangent) instead of the fp32 pointwise chain plus the casts to bf16
-            rot_dtype = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
-            q, k = apply_rotary_cast(q, cos, sin, rot_dtype), apply_rotary_cast(k, cos, sin, rot_dtype)
-            v = v.to(rot_dtype)
+            # one kernel for the split, the rotation of q and k and the cast of all three (and one for their gradients,
+            # which lands in the projection's gradient directly) instead of the fp32 pointwise chain plus the casts to bf16
+            rot_dtype = qkv.dtype if qkv.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
+            q, k, v = rotary_qkv(qkv, cos, sin, rot_dtype)
         else:
+            q, k, v = qkv.unbind(2)
             q, k = _rotate(q, cos, sin), _rotate(k, cos, sin)
         if attention in ("jvp", "lib"):
             # the library's kernels: fused JVP attention where the inputs carry forward-mode tangents, the primal-only

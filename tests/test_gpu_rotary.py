@@ -87,3 +87,46 @@ def test_unaligned_views_take_the_scalar_path():
     x = buf[..., 1:D + 1]  # row starts 2 bytes off a 16-byte boundary, row pitch not a multiple of 8 elements
     cos, sin = _tables(S, D, "cuda")
     assert torch.equal(apply_rotary_cast(x, cos, sin, torch.bfloat16), _formula(x, cos, sin).bfloat16())
+
+
+@pytest.mark.parametrize("leaf_dtype", [torch.bfloat16, torch.float32])
+def test_rotary_qkv_equals_the_per_tensor_path_under_forward_and_reverse_mode(leaf_dtype):
+    """q, k, v of one (B, S, 3, H, D) projection in one launch: outputs bit-equal to apply_rotary_cast per tensor (and a
+    plain cast for v); the gradient of the projection, written in place by one launch, equal to what autograd assembles
+    from the three per-tensor gradients."""
+    from semicat_b200 import _lib
+    from semicat_b200.rotary import rotary_qkv
+    B, S, H, D = 2, 37, 3, 64
+    g = torch.Generator(device="cuda").manual_seed(17)
+    qkv = torch.randn(B, S, 3, H, D, device="cuda", generator=g).to(leaf_dtype)
+    tqkv = torch.randn(B, S, 3, H, D, device="cuda", generator=g).to(leaf_dtype)
+    cots = [torch.randn(B, S, H, D, device="cuda", generator=g).bfloat16() for _ in range(6)]
+    cos, sin = _tables(S, D, "cuda")
+
+    def per_tensor(z):
+        q, k, v = z.unbind(2)
+        return apply_rotary_cast(q, cos, sin, torch.bfloat16), apply_rotary_cast(k, cos, sin, torch.bfloat16), v.to(torch.bfloat16)
+
+    def run(fn):
+        xl, tl = qkv.clone().requires_grad_(True), tqkv.clone().requires_grad_(True)
+        outs, touts = torch.func.jvp(fn, (xl,), (tl,))
+        grads = torch.autograd.grad(list(outs) + list(touts), [xl, tl], cots)
+        return list(outs) + list(touts) + list(grads)
+
+    before = _lib.launch_count()
+    fused = run(lambda z: rotary_qkv(z, cos, sin, torch.bfloat16))
+    assert _lib.launch_count() - before == 4  # primal and tangent forward, one launch per gradient tensor
+    plain = run(per_tensor)
+    names = ["q", "k", "v", "tq", "tk", "tv", "d qkv", "d tqkv"]
+    for name, a, b in zip(names, fused, plain):
+        assert a.dtype == b.dtype and a.shape == b.shape, name
+        assert torch.equal(a, b), f"{name}: max diff {(a.float() - b.float()).abs().max().item()}"
+    # without a tangent: one launch each way
+    xl = qkv.clone().requires_grad_(True)
+    before = _lib.launch_count()
+    q, k, v = rotary_qkv(xl, cos, sin, torch.bfloat16)
+    (dx,) = torch.autograd.grad([q, k, v], [xl], cots[:3])
+    assert _lib.launch_count() - before == 2
+    xl2 = qkv.clone().requires_grad_(True)
+    (want,) = torch.autograd.grad(list(per_tensor(xl2)), [xl2], cots[:3])
+    assert torch.equal(dx, want)
