@@ -123,3 +123,19 @@ def test_rank_failure_before_the_collective_is_reported_not_hung():
     out = _spawn(2, fail_rank=1)
     assert isinstance(out[1], str) and "injected failure" in out[1]
     assert isinstance(out[0], str), "the surviving rank should get an error from the all-reduce"
+
+
+@pytest.mark.parametrize("sd_prop", [0.0, 0.5])
+def test_noise_release_is_reported_once_and_buffers_refill_in_place(sd_prop):
+    """A training loop refills the noise buffers for the next step as soon as model_step says they are no longer read."""
+    net = _net()
+    x1, noise = _data(4)
+    calls = []
+    vf, sd = train_step.model_step(net, x1, noise, sd_prop=sd_prop, jvp_attention="math", autocast_dtype=None,
+                                   noise_released=lambda: calls.append(1))
+    train_step.total_loss(vf, sd).backward()
+    assert calls == [1]
+    before, ptr = noise["x0"].clone(), noise["x0"].data_ptr()
+    again = train_step.draw_noise(x1, VOCAB, out=noise)
+    assert again is noise and noise["x0"].data_ptr() == ptr and not torch.equal(noise["x0"], before)
+    assert noise["x0"].shape == before.shape and float(noise["t_vfm"].min()) >= 0.0 and float(noise["t_vfm"].max()) <= 1.0
